@@ -1,0 +1,305 @@
+"""Regenerates the fixtures in this folder from the reference implementation.
+
+Run in a container that has the reference checkout (default /root/reference):
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+It writes three files beside itself:
+
+  recorded_calls.npz  every call the reference's own CPU test-suite makes to
+                      _quantize_mx and _quantize_elemwise_core on the pure
+                      PyTorch path (custom_cuda=False), with the reference's
+                      output.  The reference's tests assert those outputs equal
+                      their hard-coded known answers, so a checker that matches
+                      the recorded outputs also matches those answers.
+  sweep.npz           seeded config-shaped tensors (normal, Student-t with
+                      outliers, bf16-representable, ragged shapes) through
+                      quantize_mx_op / quantize_elemwise_op for every format,
+                      rounding mode, axis, block size and scale width.
+  layers.npz          small mx.linear / matmul / bmm forward+backward cases on
+                      fp32 containers.
+
+Large arrays are stored as recipes + SHA-256 of the canonicalised output
+(NaN -> one pattern, -0 -> +0) to keep the files small.
+"""
+import argparse
+import hashlib
+import io
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+FULL_LIMIT = 4096          # arrays up to this many elements are stored whole
+
+
+def canon_bytes(a):
+    a = np.ascontiguousarray(a, np.float32).copy()
+    a[np.isnan(a)] = np.float32(np.nan)
+    a[a == 0] = 0.0
+    u = a.view(np.uint32)
+    u[np.isnan(a)] = 0x7FC00000
+    return u.tobytes()
+
+
+def sha(a):
+    return hashlib.sha256(canon_bytes(a)).hexdigest()
+
+
+def all_encodings(e, m, encodes_infs=True):
+    """Every value of an eXmY format, positives then negatives; same set as the
+    reference's mx/tests/common_lib.py:142-180 helper (written independently)."""
+    n = 1 << (e + m)
+    idx = np.arange(n)
+    if e > 0:
+        ef = idx >> m
+        mant = (idx & ((1 << m) - 1)) / float(1 << m)
+        bias = (1 << (e - 1)) - 1
+        val = np.where(ef == 0, np.ldexp(mant, 1 - bias), np.ldexp(1.0 + mant, ef - bias))
+        if encodes_infs:
+            val = np.where(ef == (1 << e) - 1, 0.0, val)
+        if e == 4 and m == 3:
+            val = np.where(idx == n - 1, 0.0, val)
+    else:
+        val = idx / float(1 << (m - 1))
+    return np.concatenate([val, -val]).astype(np.float32)
+
+
+RECIPES = {}
+
+
+def recipe_for(x):
+    """Name a large input if it is one of the all-encodings sets."""
+    if not RECIPES:
+        for (e, m, inf) in [(8, 9, True), (0, 8, False), (0, 9, False), (4, 5, False), (5, 4, True),
+                            (3, 4, False), (2, 5, False), (2, 3, False), (8, 9, False),
+                            (5, 12, True), (8, 7, True), (5, 10, True), (4, 3, False),
+                            (5, 2, True), (3, 2, False), (2, 1, False), (0, 7, False)]:
+            RECIPES[(e, m, inf)] = all_encodings(e, m, inf)
+    for k, v in RECIPES.items():
+        if v.shape == x.shape and np.array_equal(v, x, equal_nan=True):
+            return list(k)
+    return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.ref)
+    sys.dont_write_bytecode = True
+    import torch
+    torch.manual_seed(0)
+    import mx.mx_ops as mx_ops
+    import mx.elemwise_ops as ew
+
+    # ---------------------------------------------------------------- part 1
+    records, arrays, seen = [], {}, set()
+    depth = [0]
+    orig_mx, orig_core = mx_ops._quantize_mx, ew._quantize_elemwise_core
+
+    def put(name, a):
+        arrays[name] = np.ascontiguousarray(a)
+
+    def add_record(kind, x, y, params):
+        xin = x.detach().cpu().numpy().astype(np.float32)
+        yout = y.detach().cpu().numpy().astype(np.float32)
+        key = (kind, json.dumps(params, sort_keys=True), hashlib.sha256(xin.tobytes()).hexdigest())
+        if key in seen:
+            return
+        seen.add(key)
+        i = len(records)
+        rec = {"kind": kind, "params": params, "shape": list(xin.shape)}
+        if xin.size <= FULL_LIMIT:
+            put("x%d" % i, xin)
+            put("y%d" % i, yout)
+        else:
+            r = recipe_for(xin)
+            if r is None:
+                return                      # unnamed large input: not recorded
+            rec["recipe"] = r
+            rec["sha"] = sha(yout)
+        records.append(rec)
+
+    def rec_mx(A, scale_bits, elem_format, shared_exp_method="max", axes=None, block_size=0,
+               round="nearest", flush_fp32_subnorms=False, custom_cuda=False):
+        import pytest
+        if custom_cuda or A.device.type != "cpu":
+            pytest.skip("native back-end not recorded")
+        depth[0] += 1
+        try:
+            y = orig_mx(A, scale_bits, elem_format, shared_exp_method, axes, block_size, round,
+                        flush_fp32_subnorms, False)
+        finally:
+            depth[0] -= 1
+        if depth[0] == 0 and elem_format is not None and A.dtype == torch.float32:
+            ax = [axes] if isinstance(axes, int) else list(axes)
+            if len(ax) == 1 and shared_exp_method == "max":
+                add_record("mx", A, y, {"scale_bits": scale_bits, "fmt": str(elem_format).split(".")[-1],
+                                        "axis": int(ax[0]), "block": int(block_size), "round": round,
+                                        "flush": bool(flush_fp32_subnorms)})
+        return y
+
+    def rec_core(A, bits, exp_bits, max_norm, round="nearest", saturate_normals=False,
+                 allow_denorm=True, custom_cuda=False):
+        import pytest
+        if custom_cuda or A.device.type != "cpu":
+            pytest.skip("native back-end not recorded")
+        depth[0] += 1
+        try:
+            y = orig_core(A, bits, exp_bits, max_norm, round, saturate_normals, allow_denorm, False)
+        finally:
+            depth[0] -= 1
+        if depth[0] == 0 and A.dtype == torch.float32 and round != "dither":
+            add_record("elem", A, y, {"bits": int(bits), "exp_bits": int(exp_bits),
+                                      "max_norm": float(max_norm), "round": round,
+                                      "saturate": bool(saturate_normals),
+                                      "allow_denorm": bool(allow_denorm)})
+        return y
+
+    mx_ops._quantize_mx = rec_mx
+    ew._quantize_elemwise_core = rec_core
+    mx_ops._quantize_elemwise_core = rec_core
+    import pytest
+    cwd = os.getcwd()
+    os.chdir(args.ref)
+    files = ["mx/tests/test_%s.py" % n for n in
+             ("e5m0_scale", "fp8_e4m3_fix", "quantize_mx", "quantize_elemwise", "corners_mx",
+              "corners_elemwise")]
+    buf = io.StringIO()
+    rc = pytest.main(["-p", "no:cacheprovider", "-q", "-x", "--no-header", "-k",
+                      "not cuda and not empty and not test_mxfp8_e4m3_round"] + files)
+    os.chdir(cwd)
+    mx_ops._quantize_mx, ew._quantize_elemwise_core = orig_mx, orig_core
+    mx_ops._quantize_elemwise_core = orig_core
+    print("reference test run rc =", rc, "records:", len(records))
+
+    # the one known-answer test that allocates a CUDA tensor it never uses
+    # (mx/tests/test_fp8_e4m3_fix.py:88-119): call its math directly.
+    import ast
+    src = open(os.path.join(args.ref, "mx/tests/test_fp8_e4m3_fix.py")).read()
+    fn = [n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef)
+          and n.name == "test_mxfp8_e4m3_round"][0]
+    vals = {}
+    for st in fn.body:
+        if isinstance(st, ast.Assign) and st.targets[0].id in ("x_", "t_"):
+            vals[st.targets[0].id] = np.array(ast.literal_eval(st.value), np.float32)
+    for rnd in ("nearest", "even"):
+        xt = torch.tensor(vals["x_"])
+        y = orig_mx(xt, 8, "fp8_e4m3", block_size=32, axes=0, round=rnd)
+        assert np.array_equal(y.numpy(), vals["t_"])
+        add_record("mx", xt, y, {"scale_bits": 8, "fmt": "fp8_e4m3", "axis": 0, "block": 32,
+                                 "round": rnd, "flush": False})
+
+    np.savez_compressed(os.path.join(HERE, "recorded_calls.npz"),
+                        meta=np.frombuffer(json.dumps(records).encode(), np.uint8), **arrays)
+
+    # ---------------------------------------------------------------- part 2
+    from mx.specs import finalize_mx_specs
+    from mx.mx_ops import quantize_mx_op
+    from mx.elemwise_ops import quantize_elemwise_op, _quantize_bfloat, _quantize_fp
+    g = torch.Generator().manual_seed(1234)
+    inputs = {}
+    inputs["normal_64x96"] = torch.randn(64, 96, generator=g)
+    t = torch.distributions.StudentT(3.0).sample((96, 128))
+    mask = torch.rand(96, 128, generator=g) < 1e-2
+    inputs["studentt_outliers_96x128_bf16vals"] = torch.where(mask, t * 1e3, t).to(torch.bfloat16).float()
+    inputs["ragged_3x37x50"] = torch.randn(3, 37, 50, generator=g) * 4
+    wide = torch.randn(32, 64, generator=g) * torch.exp2(torch.randint(-140, 120, (32, 64), generator=g).float())
+    wide[3, 5] = float("inf"); wide[7, 9] = float("nan"); wide[11, :] = 0
+    inputs["wide_range_32x64"] = wide
+    tiny = torch.randn(16, 64, generator=g) * 2.0 ** -130
+    inputs["fp32_subnormals_16x64"] = tiny
+    sweep_meta, sweep_arr = [], {}
+    for name, x in inputs.items():
+        sweep_arr["in_" + name] = x.numpy()
+    for name, x in inputs.items():
+        for fmt in ("fp8_e4m3", "fp8_e5m2", "fp6_e3m2", "fp6_e2m3", "fp4_e2m1", "int8", "int4", "int2"):
+            for rnd in ("nearest", "floor", "even"):
+                for axis in range(-x.ndim, 0):
+                    for block in (32, 16, 9, 0):
+                        for sb in (8, 5):
+                            for flush in (False, True):
+                                if flush and (block != 32 or rnd != "nearest"):
+                                    continue
+                                if sb == 5 and block not in (32, 9):
+                                    continue
+                                specs = finalize_mx_specs({"a_elem_format": fmt, "scale_bits": sb,
+                                                           "block_size": block,
+                                                           "mx_flush_fp32_subnorms": flush,
+                                                           "custom_cuda": False})
+                                y = quantize_mx_op(x.clone(), specs, elem_format=fmt, axes=[axis], round=rnd)
+                                sweep_meta.append({"kind": "mx", "in": name, "fmt": fmt, "round": rnd,
+                                                   "axis": axis, "block": block, "scale_bits": sb,
+                                                   "flush": flush, "sha": sha(y.numpy())})
+        for spec_kind, val in (("bfloat", 16), ("bfloat", 12), ("bfloat", 10), ("fp", 16), ("fp", 12), ("fp", 8)):
+            for rnd in ("nearest", "floor", "even"):
+                for sub in (True, False):
+                    if spec_kind == "bfloat":
+                        y = _quantize_bfloat(x.clone(), val, round=rnd, allow_denorm=sub)
+                    else:
+                        y = _quantize_fp(x.clone(), exp_bits=5, mantissa_bits=val - 6, round=rnd, allow_denorm=sub)
+                    sweep_meta.append({"kind": "elem", "in": name, "spec": spec_kind, "val": val, "round": rnd,
+                                       "subnorms": sub, "sha": sha(y.numpy())})
+    np.savez_compressed(os.path.join(HERE, "sweep.npz"),
+                        meta=np.frombuffer(json.dumps(sweep_meta).encode(), np.uint8), **sweep_arr)
+    print("sweep cases:", len(sweep_meta))
+
+    # ---------------------------------------------------------------- part 3
+    import mx
+    lay = {}
+    lmeta = []
+
+    def bf(x):
+        return x.to(torch.bfloat16).float()
+
+    def run_linear(tag, specs, M, K, N, bias, lead=()):
+        sp = finalize_mx_specs(dict(specs, custom_cuda=False))
+        x = bf(torch.randn(*lead, M, K, generator=g)).requires_grad_()
+        w = bf((torch.rand(N, K, generator=g) * 2 - 1) / K ** 0.5).requires_grad_()
+        b = bf(torch.randn(N, generator=g) * 0.1).requires_grad_() if bias else None
+        go = bf(torch.randn(*lead, M, N, generator=g))
+        y = mx.linear(x, w, b, mx_specs=sp)
+        y.backward(go)
+        lay[tag + "_x"], lay[tag + "_w"], lay[tag + "_go"] = x.detach().numpy(), w.detach().numpy(), go.numpy()
+        lay[tag + "_y"], lay[tag + "_gx"], lay[tag + "_gw"] = y.detach().numpy(), x.grad.numpy(), w.grad.numpy()
+        if bias:
+            lay[tag + "_b"], lay[tag + "_gb"] = b.detach().numpy(), b.grad.numpy()
+        lmeta.append({"op": "linear", "tag": tag, "specs": specs, "bias": bias})
+
+    def run_mm(tag, specs, op, B, M, K, N):
+        sp = finalize_mx_specs(dict(specs, custom_cuda=False))
+        a = bf(torch.randn(*B, M, K, generator=g)).requires_grad_()
+        b = bf(torch.randn(*B, K, N, generator=g)).requires_grad_()
+        go = bf(torch.randn(*B, M, N, generator=g))
+        y = (mx.bmm if op == "bmm" else mx.matmul)(a, b, mx_specs=sp)
+        y.backward(go)
+        lay[tag + "_a"], lay[tag + "_b"], lay[tag + "_go"] = a.detach().numpy(), b.detach().numpy(), go.numpy()
+        lay[tag + "_y"], lay[tag + "_ga"], lay[tag + "_gb"] = y.detach().numpy(), a.grad.numpy(), b.grad.numpy()
+        lmeta.append({"op": op, "tag": tag, "specs": specs})
+
+    s_fp8 = {"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "w_elem_format_bp": "fp8_e5m2",
+             "a_elem_format_bp": "fp8_e5m2", "a_elem_format_bp_ex": "fp8_e5m2",
+             "a_elem_format_bp_os": "fp8_e5m2", "block_size": 32, "scale_bits": 8, "bfloat": 16}
+    s_fp4 = {"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32,
+             "scale_bits": 8, "bfloat": 16}
+    s_fp6 = {"w_elem_format": "fp6_e3m2", "a_elem_format": "fp6_e3m2", "block_size": 32,
+             "scale_bits": 8, "bfloat": 16}
+    s_int8 = {"w_elem_format": "int8", "a_elem_format": "int8", "block_size": 32, "scale_bits": 8,
+              "bfloat": 16, "round": "even"}
+    run_linear("lin_fp8", s_fp8, 128, 256, 192, False)
+    run_linear("lin_fp8_bias3d", s_fp8, 64, 128, 96, True, lead=(2,))
+    run_linear("lin_fp4w", s_fp4, 128, 256, 128, False)
+    run_linear("lin_int8_even", s_int8, 64, 128, 64, True)
+    run_mm("bmm_fp6", s_fp6, "bmm", (3,), 64, 128, 96)
+    run_mm("matmul_fp8", s_fp8, "matmul", (), 96, 64, 128)
+    run_mm("matmul_fp6_4d", s_fp6, "matmul", (2, 2), 32, 64, 32)
+    np.savez_compressed(os.path.join(HERE, "layers.npz"),
+                        meta=np.frombuffer(json.dumps(lmeta).encode(), np.uint8), **lay)
+    print("layer cases:", len(lmeta))
+
+
+if __name__ == "__main__":
+    main()
