@@ -1,0 +1,186 @@
+"""ctypes binding of libmxq.so: the only way the Python layer reaches the GPU.
+
+Takes the place of the reference's mx/custom_extensions.py (a
+torch.utils.cpp_extension JIT build).  The library is prebuilt in-tree by
+``python -m microxcaling_b200.build``; there is no CPU or eager fallback for CUDA
+tensors: if the library is missing, loading raises.
+
+``funcs`` keeps the seven names the reference's pybind module exports
+(mx/cpp/funcs.cpp:234-242) so reference-style callers keep working.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libmxq.so")
+_lib = None
+
+F32, F16, BF16 = 0, 1, 2
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+ROUND_DITHER = 3
+CODES_TRANSPOSED = 1
+
+
+class MxqError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise MxqError("libmxq.so not built: run `python -m microxcaling_b200.build` "
+                           "(needs nvcc with sm_100a support)")
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+        L.mxq_status_string.restype = ctypes.c_char_p
+        L.mxq_status_string.argtypes = [i32]
+        L.mxq_quantize_mx.argtypes = [vp, vp, vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32,
+                                      i32, i32, vp, i32, vp]
+        L.mxq_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, vp]
+        L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
+        L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
+        _lib = L
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        raise MxqError("libmxq: %s (status %d)" % (lib().mxq_status_string(status).decode(), status))
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(t, name="tensor"):
+    if not t.is_cuda:
+        raise MxqError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise MxqError("%s must be contiguous" % name)
+    if t.dtype not in _DT:
+        raise MxqError("Tensor dtype not supported: %s" % t.dtype)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else None
+
+
+def _split(shape, axis):
+    pre = 1
+    for s in shape[:axis]:
+        pre *= s
+    post = 1
+    for s in shape[axis + 1:]:
+        post *= s
+    return pre, shape[axis], post
+
+
+def quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False, rmode=0,
+                noise=None, want_dq=True, want_codes=False, transposed=False):
+    """MX-quantize CUDA tensor A in blocks of `block` along `axis`.
+
+    Returns the dequantized tensor (A's dtype), or with want_codes a tuple
+    (dq or None, codes uint8, scales uint8).  Codes/scales layouts are those of
+    mxq_quantize_mx in include/mxq.h."""
+    _require_cuda(A, "A")
+    axis = axis % A.dim() if A.dim() else 0
+    shape = list(A.shape)
+    pre, n, post = _split(shape, axis)
+    blk = int(block) if block and block > 0 else n
+    blk = min(blk, n) if n > 0 else 1
+    nblk = (n + blk - 1) // blk if n else 0
+    out = torch.empty_like(A) if want_dq else None
+    codes = scales = None
+    if want_codes:
+        if transposed:
+            codes = torch.empty(shape[:axis] + shape[axis + 1:] + [nblk * blk], dtype=torch.uint8, device=A.device)
+            scales = torch.empty(shape[:axis] + shape[axis + 1:] + [nblk], dtype=torch.uint8, device=A.device)
+        else:
+            codes = torch.empty(shape, dtype=torch.uint8, device=A.device)
+            scales = torch.empty(shape[:axis] + [nblk] + shape[axis + 1:], dtype=torch.uint8, device=A.device)
+    if noise is not None:
+        _require_cuda(noise, "noise")
+        assert noise.dtype == torch.float32 and noise.shape == A.shape
+    with torch.cuda.device(A.device):
+        check(lib().mxq_quantize_mx(_ptr(A), _ptr(out), _ptr(codes), _ptr(scales), _DT[A.dtype],
+                                    pre, n, post, blk, int(scale_bits), int(ebits), int(mbits),
+                                    float(max_norm), int(bool(flush)), int(rmode), _ptr(noise),
+                                    CODES_TRANSPOSED if transposed else 0, _stream(A)))
+    if want_codes:
+        return out, codes, scales
+    return out
+
+
+def quantize_elemwise(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=False,
+                      allow_denorm=True, noise=None, out_dtype=None):
+    _require_cuda(A, "A")
+    out = torch.empty_like(A) if out_dtype in (None, A.dtype) else \
+        torch.empty(A.shape, dtype=out_dtype, device=A.device)
+    if bits > 24:
+        raise MxqError("quantize_elemwise with bits > 24 leads to negative shifts")
+    if noise is not None:
+        _require_cuda(noise, "noise")
+    with torch.cuda.device(A.device):
+        check(lib().mxq_quantize_elemwise(_ptr(A), _ptr(out), _DT[A.dtype], _DT[out.dtype], A.numel(),
+                                          int(bits), int(exp_bits), float(max_norm), int(rmode),
+                                          int(bool(saturate_normals)), int(bool(allow_denorm)),
+                                          _ptr(noise), _stream(A)))
+    return out
+
+
+def _reduce(A, fn):
+    _require_cuda(A, "A")
+    if A.dtype != torch.float32:
+        raise MxqError("reduce over the inner dim supports float32 only")
+    inner = A.shape[-1]
+    rows = A.numel() // inner if inner else 0
+    out = torch.empty(A.shape[:-1], dtype=A.dtype, device=A.device)
+    with torch.cuda.device(A.device):
+        check(fn(_ptr(A), _ptr(out), rows, inner, _stream(A)))
+    return out
+
+
+class _Funcs:
+    """The reference extension's exported names on top of the C ABI."""
+
+    @staticmethod
+    def quantize_mx_by_tile_func_cuda(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm,
+                                      tile_size, axis, flush_fp32_subnorms=False, rmode=0):
+        if axis >= A.dim():
+            raise MxqError("quantize_mx_by_tile axis exceeds input dimensions")
+        return quantize_mx(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm, tile_size, axis,
+                           flush_fp32_subnorms, int(rmode))
+
+    @staticmethod
+    def quantize_mx_func_cuda(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm, max_values,
+                              axis, flush_fp32_subnorms=False, rmode=0):
+        # the whole `axis` is one block; its maximum is recomputed in-kernel
+        if axis >= A.dim():
+            raise MxqError("quantize_mx_func_cuda axis exceeds input dimensions")
+        return quantize_mx(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm, 0, axis,
+                           flush_fp32_subnorms, int(rmode))
+
+    @staticmethod
+    def quantize_elemwise_func_cuda(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=False,
+                                    allow_denorm=True):
+        return quantize_elemwise(A, bits, exp_bits, max_norm, int(rmode), saturate_normals, allow_denorm)
+
+    @staticmethod
+    def quantize_mx_func_cpp(*args, **kwargs):
+        raise MxqError("this back-end has no host (C++) quantizer: move the tensor to a CUDA device")
+
+    quantize_elemwise_func_cpp = quantize_mx_func_cpp
+
+    @staticmethod
+    def reduce_sum_inner_dim(A):
+        return _reduce(A, lib().mxq_reduce_sum_inner)
+
+    @staticmethod
+    def reduce_max_inner_dim(A):
+        return _reduce(A, lib().mxq_reduce_max_inner)
+
+
+funcs = _Funcs()

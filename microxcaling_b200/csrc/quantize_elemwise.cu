@@ -1,0 +1,173 @@
+// Elementwise format rounding (bfloatX / fpX / arbitrary eXmY) for sm_100a.
+//
+// One streaming kernel: each thread converts eight consecutive elements per
+// step (16- or 32-byte vector loads and stores), grid sized from the SM count.
+// Formats with eight exponent bits (the bfloat family, which is what the MX
+// layers use between GEMMs) share fp32's exponent layout, subnormals included,
+// so rounding is an integer add-and-mask on the raw bits; every other format
+// goes through the exact integer routine of mxq_math.cuh.
+#include "mxq_common.cuh"
+#include <algorithm>
+#include <cstring>
+
+namespace mxq {
+
+struct EwArgs {
+    const void* in;
+    void* out;
+    const float* noise;
+    int64_t n;
+    int bits, exp_bits;
+    float max_norm;
+    int mode;
+    int saturate, allow_denorm;
+    uint32_t drop;          // low bits removed (8-exponent-bit path)
+    uint32_t max_bits;      // bit pattern of max_norm
+};
+
+// fp32 bit pattern -> rounded fp32 bit pattern, formats with 8 exponent bits
+template <int MODE>
+__device__ __forceinline__ uint32_t round_bf_family(uint32_t u, const EwArgs& a) {
+    const uint32_t mag = u & 0x7fffffffu;
+    const uint32_t sgn = u & 0x80000000u;
+    if (mag >= kInf) return mag > kInf ? kNaN : u;
+    if (!a.allow_denorm && mag < 0x00800000u) return mag == 0 ? 0u : sgn;
+    const uint32_t mask = (1u << a.drop) - 1u;
+    uint32_t r = mag;
+    if (MODE == RN_AWAY) r += 1u << (a.drop - 1);
+    else if (MODE == RN_EVEN) r += (mask >> 1) + ((mag >> a.drop) & 1u);
+    r &= ~mask;
+    if (r > a.max_bits) r = a.saturate ? a.max_bits : kInf;
+    return (r == 0 && mag == 0) ? 0u : (r | sgn);
+}
+
+template <int IN_DT, int N> struct Load8;
+template <> struct Load8<DT_F32, 8> {
+    static __device__ __forceinline__ void run(const void* p, int64_t e, uint32_t (&b)[8]) {
+        uint32_t lo[4], hi[4];
+        VecIO<DT_F32, 16>::load(p, e, lo);
+        VecIO<DT_F32, 16>::load(p, e + 4, hi);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { b[i] = lo[i]; b[4 + i] = hi[i]; }
+    }
+};
+template <> struct Load8<DT_BF16, 8> {
+    static __device__ __forceinline__ void run(const void* p, int64_t e, uint32_t (&b)[8]) { VecIO<DT_BF16, 16>::load(p, e, b); }
+};
+template <> struct Load8<DT_F16, 8> {
+    static __device__ __forceinline__ void run(const void* p, int64_t e, uint32_t (&b)[8]) { VecIO<DT_F16, 16>::load(p, e, b); }
+};
+
+template <int OUT_DT> __device__ __forceinline__ void store8(void* p, int64_t e, const uint32_t (&b)[8]);
+template <> __device__ __forceinline__ void store8<DT_F32>(void* p, int64_t e, const uint32_t (&b)[8]) {
+    float* o = reinterpret_cast<float*>(p) + e;
+    reinterpret_cast<uint4*>(o)[0] = make_uint4(b[0], b[1], b[2], b[3]);
+    reinterpret_cast<uint4*>(o)[1] = make_uint4(b[4], b[5], b[6], b[7]);
+}
+template <> __device__ __forceinline__ void store8<DT_BF16>(void* p, int64_t e, const uint32_t (&b)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]));
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p) + e) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <> __device__ __forceinline__ void store8<DT_F16>(void* p, int64_t e, const uint32_t (&b)[8]) {
+    VecIO<DT_F16, 16>::store(p, e, b);
+}
+
+// PATH 0: 8-exponent-bit integer rounding; PATH 1: exact generic routine
+template <int IN_DT, int OUT_DT, int PATH, int MODE>
+__device__ __forceinline__ uint32_t ew_one(uint32_t u, const EwArgs& a, int64_t idx) {
+    if (PATH == 0) return round_bf_family<MODE>(u, a);
+    return __float_as_uint(round_generic(__uint_as_float(u), a.bits, a.exp_bits, a.max_norm, a.mode,
+                                         a.saturate != 0, a.allow_denorm != 0,
+                                         a.noise ? a.noise[idx] : 0.f));
+}
+
+constexpr int kEwThreads = 256;
+
+template <int IN_DT, int OUT_DT, int PATH, int MODE>
+__global__ void __launch_bounds__(kEwThreads)
+ew_vec_kernel(const EwArgs a, const int64_t nvec8) {
+    const int64_t stride = (int64_t)gridDim.x * kEwThreads;
+    for (int64_t v = (int64_t)blockIdx.x * kEwThreads + threadIdx.x; v < nvec8; v += stride) {
+        uint32_t b[8];
+        Load8<IN_DT, 8>::run(a.in, v * 8, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = ew_one<IN_DT, OUT_DT, PATH, MODE>(b[i], a, v * 8 + i);
+        store8<OUT_DT>(a.out, v * 8, b);
+    }
+}
+
+template <int IN_DT, int OUT_DT, int PATH, int MODE>
+__global__ void ew_scalar_kernel(const EwArgs a, const int64_t first, const int64_t n) {
+    const int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t u = __float_as_uint(load1<IN_DT>(a.in, i));
+    store1<OUT_DT>(a.out, i, __uint_as_float(ew_one<IN_DT, OUT_DT, PATH, MODE>(u, a, i)));
+}
+
+template <int IN_DT, int OUT_DT, int PATH, int MODE>
+static int launch_ew(const EwArgs& a, cudaStream_t st) {
+    const bool vec_ok = aligned16(a.in) && aligned16(a.out);
+    const int64_t nvec8 = vec_ok ? a.n / 8 : 0;
+    if (nvec8 > 0) {
+        const int64_t need = (nvec8 + kEwThreads - 1) / kEwThreads;
+        const int grid = (int)std::min<int64_t>(need, (int64_t)sm_count() * 32);
+        ew_vec_kernel<IN_DT, OUT_DT, PATH, MODE><<<grid, kEwThreads, 0, st>>>(a, nvec8);
+    }
+    const int64_t first = nvec8 * 8;
+    if (first < a.n) {
+        const int64_t rest = a.n - first;
+        const int64_t grid = (rest + 127) / 128;
+        if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+        ew_scalar_kernel<IN_DT, OUT_DT, PATH, MODE><<<(unsigned)grid, 128, 0, st>>>(a, first, a.n);
+    }
+    return check_launch();
+}
+
+template <int IN_DT, int OUT_DT>
+static int dispatch_path(const EwArgs& a, cudaStream_t st) {
+    if (a.exp_bits == 8 && a.mode <= RN_EVEN) {
+        switch (a.mode) {
+            case RN_AWAY: return launch_ew<IN_DT, OUT_DT, 0, RN_AWAY>(a, st);
+            case RZ:      return launch_ew<IN_DT, OUT_DT, 0, RZ>(a, st);
+            default:      return launch_ew<IN_DT, OUT_DT, 0, RN_EVEN>(a, st);
+        }
+    }
+    return launch_ew<IN_DT, OUT_DT, 1, 0>(a, st);
+}
+
+}  // namespace mxq
+
+extern "C" int mxq_quantize_elemwise(const void* in, void* out, int in_dtype, int out_dtype, int64_t n,
+                                     int bits, int exp_bits, float max_norm, int rmode,
+                                     int saturate_normals, int allow_denorm, const void* noise,
+                                     void* stream) {
+    using namespace mxq;
+    if (n < 0) return MXQ_ERR_BAD_ARG;
+    if (n == 0) return MXQ_OK;
+    if (!in || !out) return MXQ_ERR_BAD_ARG;
+    if (bits < 2 || bits > 24 || exp_bits < 0 || exp_bits > 8) return MXQ_ERR_BAD_ARG;  // funcs.cpp:209
+    if (rmode < MXQ_ROUND_NEAREST || rmode > MXQ_ROUND_DITHER) return MXQ_ERR_BAD_ARG;
+    if (rmode == MXQ_ROUND_DITHER && !noise) return MXQ_ERR_BAD_ARG;
+    EwArgs a;
+    a.in = in; a.out = out; a.noise = (const float*)noise; a.n = n;
+    a.bits = bits; a.exp_bits = exp_bits; a.max_norm = max_norm; a.mode = rmode;
+    a.saturate = saturate_normals != 0; a.allow_denorm = allow_denorm != 0;
+    a.drop = (uint32_t)(24 - (bits - 1));
+    memcpy(&a.max_bits, &max_norm, 4);
+    cudaStream_t st = (cudaStream_t)stream;
+#define MXQ_EW_CASE(I, O) if (in_dtype == I && out_dtype == O) return dispatch_path<I, O>(a, st)
+    MXQ_EW_CASE(DT_F32, DT_F32);
+    MXQ_EW_CASE(DT_BF16, DT_BF16);
+    MXQ_EW_CASE(DT_F16, DT_F16);
+    MXQ_EW_CASE(DT_F32, DT_BF16);
+    MXQ_EW_CASE(DT_F32, DT_F16);
+    MXQ_EW_CASE(DT_BF16, DT_F32);
+    MXQ_EW_CASE(DT_F16, DT_F32);
+#undef MXQ_EW_CASE
+    return MXQ_ERR_UNSUPPORTED;
+}

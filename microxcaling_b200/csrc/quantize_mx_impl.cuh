@@ -1,0 +1,352 @@
+// MX block quantization kernels (sm_100a) and their C entry point.
+//
+// Three kernels share one per-element routine:
+//   mx_lastaxis_kernel  blocks along the contiguous axis: each thread owns one
+//                       16-byte vector, the block maximum is a butterfly of
+//                       warp shuffles over the lanes that share a block, the
+//                       tensor is read once and written once.
+//   mx_strided_kernel   blocks along an outer axis (stride `post`): each thread
+//                       owns an 8-byte column strip and keeps all rows of the
+//                       block in registers, so the column maxima need no
+//                       communication and the input is read exactly once.  The
+//                       same kernel can write the packed operand transposed
+//                       (blocked axis innermost), which is the layout the
+//                       backward GEMMs need.
+//   mx_generic_kernel   one thread per block, any shape / block size / mode;
+//                       used for ragged, unaligned or very wide cases.
+// HBM-bound: the arithmetic per element is one multiply into the scaled
+// domain, the add-subtract grid rounding of mxq_math.cuh, one multiply back.
+#pragma once
+#include "mxq_common.cuh"
+#include <algorithm>
+#include <cstring>
+
+namespace mxq {
+
+struct MxArgs {
+    const void* in;
+    void* out;
+    uint8_t* codes;
+    uint8_t* scales;
+    const float* noise;
+    int64_t pre, axis_len, post;
+    int64_t nblk;
+    int block;
+    int scale_emax;
+    int flush;
+    int mode;
+    int transposed;
+    ElemFmt fmt;
+};
+
+// Per-block constants derived from the block's absolute maximum.
+struct BlockScale {
+    float scale;   // 2^(E-127), NaN when the block is NaN
+    float inv;     // 2^(127-E), 0 when the block is flushed or NaN
+    int E;
+};
+
+__device__ __forceinline__ BlockScale block_scale(uint32_t amax_bits, const MxArgs& a) {
+    BlockScale s;
+    const int E = scale_exp_from_absmax(amax_bits, a.fmt.emax_elem, a.scale_emax);
+    const bool nan_blk = (E == 255);
+    const bool flush = a.flush && (amax_bits >> 23) == 0;
+    s.E = E;
+    s.scale = nan_blk ? __uint_as_float(kNaN) : pow2_from_field(E);
+    s.inv = (nan_blk || flush) ? 0.0f : inv_pow2_from_field(E);
+    return s;
+}
+
+// x (fp32 bits) -> scaled rounded magnitude q (>= 0); the dequantized bits are
+// (q * scale) | sign.
+template <int MODE>
+__device__ __forceinline__ float quant_abs(uint32_t xb, const BlockScale& s, const ElemFmt& f) {
+    const float v = __uint_as_float(xb & 0x7fffffffu) * s.inv;
+    return round_grid_abs<MODE>(__float_as_uint(v), f.emin_field, f.k_field, f.max_norm);
+}
+
+__device__ __forceinline__ uint32_t pack_codes4(const float* q, const uint32_t* xb, const ElemFmt& f) {
+    // four signed scaled values -> four code bytes (little endian)
+    float s[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = __uint_as_float(__float_as_uint(q[i]) | (xb[i] & 0x80000000u));
+    if (f.ebits == 0) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r |= (uint32_t)(__float2int_rn(ldexpf(s[i], f.mbits - 2)) & 0xff) << (8 * i);
+        return r;
+    }
+    if (f.ebits == 5) return encode2_e5m2(s[0], s[1]) | (encode2_e5m2(s[2], s[3]) << 16);
+    return encode2_e4m3(s[0], s[1]) | (encode2_e4m3(s[2], s[3]) << 16);
+}
+
+// ---------------------------------------------------------------------------
+// last-axis kernel
+// ---------------------------------------------------------------------------
+constexpr int kLastThreads = 256;
+constexpr int kLastUnroll = 4;
+
+template <int DT, int MODE, bool WANT_DQ, bool WANT_CODES>
+__global__ void __launch_bounds__(kLastThreads)
+mx_lastaxis_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block) {
+    using IO = VecIO<DT, 16>;
+    constexpr int N = IO::N;
+    const int64_t tile = (int64_t)kLastThreads * kLastUnroll;
+    for (int64_t base = (int64_t)blockIdx.x * tile; base < nvec; base += (int64_t)gridDim.x * tile) {
+        uint32_t xb[kLastUnroll][N];
+        bool live[kLastUnroll];
+#pragma unroll
+        for (int u = 0; u < kLastUnroll; ++u) {
+            const int64_t v = base + (int64_t)u * kLastThreads + threadIdx.x;
+            live[u] = v < nvec;
+            if (live[u]) IO::load(a.in, v * N, xb[u]);
+            else {
+#pragma unroll
+                for (int i = 0; i < N; ++i) xb[u][i] = 0;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kLastUnroll; ++u) {
+            const int64_t v = base + (int64_t)u * kLastThreads + threadIdx.x;
+            uint32_t m = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i) m = max(m, xb[u][i] & 0x7fffffffu);   // NaN bits compare largest
+            for (int s = 1; s < lanes_per_block; s <<= 1)
+                m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+            const BlockScale bs = block_scale(m, a);
+            float q[N];
+#pragma unroll
+            for (int i = 0; i < N; ++i) q[i] = quant_abs<MODE>(xb[u][i], bs, a.fmt);
+            if (!live[u]) continue;
+            if (WANT_CODES) {
+                uint32_t c[N / 4];
+#pragma unroll
+                for (int i = 0; i < N / 4; ++i) c[i] = pack_codes4(&q[4 * i], &xb[u][4 * i], a.fmt);
+                if (N == 4) *reinterpret_cast<uint32_t*>(a.codes + v * N) = c[0];
+                else *reinterpret_cast<uint2*>(a.codes + v * N) = make_uint2(c[0], c[N / 4 - 1]);
+                if ((threadIdx.x & (lanes_per_block - 1)) == 0) a.scales[v / lanes_per_block] = (uint8_t)bs.E;
+            }
+            if (WANT_DQ) {
+                uint32_t ob[N];
+#pragma unroll
+                for (int i = 0; i < N; ++i)
+                    ob[i] = __float_as_uint(q[i] * bs.scale) | (xb[u][i] & 0x80000000u);
+                IO::store(a.out, v * N, ob);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// strided-axis kernel: thread = 8-byte column strip x up to 32 rows
+// ---------------------------------------------------------------------------
+constexpr int kStrThreads = 128;
+constexpr int kMaxRows = 32;
+
+template <int DT, int MODE, bool WANT_DQ, bool WANT_CODES>
+__global__ void __launch_bounds__(kStrThreads)
+mx_strided_kernel(const MxArgs a, const int64_t col_tiles, const int64_t ntiles) {
+    using IO = VecIO<DT, 8>;
+    constexpr int N = IO::N;
+    const int64_t cols_per_cta = (int64_t)kStrThreads * N;
+    for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int64_t ct = t % col_tiles;
+        const int64_t pb = t / col_tiles;                 // pre * nblk index
+        const int64_t b = pb % a.nblk;
+        const int64_t p = pb / a.nblk;
+        const int64_t col = ct * cols_per_cta + (int64_t)threadIdx.x * N;
+        if (col >= a.post) continue;
+        const int64_t row0 = b * a.block;
+        const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
+        const int64_t base = (p * a.axis_len + row0) * a.post + col;
+        uint32_t xb[kMaxRows][N];
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) {
+            if (r < rows) IO::load(a.in, base + (int64_t)r * a.post, xb[r]);
+            else {
+#pragma unroll
+                for (int i = 0; i < N; ++i) xb[r][i] = 0;
+            }
+        }
+        uint32_t m[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) m[i] = 0;
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r)
+#pragma unroll
+            for (int i = 0; i < N; ++i) m[i] = max(m[i], xb[r][i] & 0x7fffffffu);
+        BlockScale bs[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) bs[i] = block_scale(m[i], a);
+
+        if (WANT_CODES && !a.transposed) {
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+                a.scales[(p * a.nblk + b) * a.post + col + i] = (uint8_t)bs[i].E;
+        }
+        if (WANT_CODES && a.transposed) {
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+                a.scales[(p * a.post + col + i) * a.nblk + b] = (uint8_t)bs[i].E;
+        }
+        // transposed codes: 32 bytes per column, rows innermost
+        uint32_t tc[N][kMaxRows / 4];
+#pragma unroll
+        for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
+            float q[4][N];
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+                const int r = r4 * 4 + rr;
+#pragma unroll
+                for (int i = 0; i < N; ++i) q[rr][i] = quant_abs<MODE>(xb[r][i], bs[i], a.fmt);
+                if (WANT_DQ && r < rows) {
+                    uint32_t ob[N];
+#pragma unroll
+                    for (int i = 0; i < N; ++i)
+                        ob[i] = __float_as_uint(q[rr][i] * bs[i].scale) | (xb[r][i] & 0x80000000u);
+                    IO::store(a.out, base + (int64_t)r * a.post, ob);
+                }
+                if (WANT_CODES && !a.transposed && r < rows) {
+                    // row-major codes: N bytes per thread per row
+                    float qq[4]; uint32_t xx[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { qq[i] = q[rr][i < N ? i : 0]; xx[i] = xb[r][i < N ? i : 0]; }
+                    const uint32_t c = pack_codes4(qq, xx, a.fmt);
+                    if (N == 4) *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c;
+                    else *reinterpret_cast<uint16_t*>(a.codes + base + (int64_t)r * a.post) = (uint16_t)c;
+                }
+            }
+            if (WANT_CODES && a.transposed) {
+#pragma unroll
+                for (int i = 0; i < N; ++i) {
+                    float qq[4]; uint32_t xx[4];
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) { qq[rr] = q[rr][i]; xx[rr] = xb[r4 * 4 + rr][i]; }
+                    tc[i][r4] = pack_codes4(qq, xx, a.fmt);
+                }
+            }
+        }
+        if (WANT_CODES && a.transposed) {
+            // [pre, post, nblk*block]: the block's bytes are contiguous
+            const int64_t padded = a.nblk * a.block;
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                uint8_t* dst = a.codes + (p * a.post + col + i) * padded + row0;
+                if (a.block == kMaxRows && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
+                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(tc[i][4], tc[i][5], tc[i][6], tc[i][7]);
+                } else {
+                    for (int r = 0; r < a.block; ++r) dst[r] = (uint8_t)(tc[i][r >> 2] >> (8 * (r & 3)));
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// generic kernel: one thread per block of the tensor
+// ---------------------------------------------------------------------------
+template <int DT>
+__global__ void mx_generic_kernel(const MxArgs a, const int64_t ntiles) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= ntiles) return;
+    const int64_t j = t % a.post;
+    const int64_t b = (t / a.post) % a.nblk;
+    const int64_t p = t / (a.post * a.nblk);
+    const int64_t k0 = b * a.block;
+    const int64_t k1 = min(k0 + a.block, a.axis_len);
+    const int64_t base = p * a.axis_len * a.post + j;
+    uint32_t m = 0;
+    for (int64_t k = k0; k < k1; ++k)
+        m = max(m, __float_as_uint(load1<DT>(a.in, base + k * a.post)) & 0x7fffffffu);
+    const BlockScale bs = block_scale(m, a);
+    const bool dead = bs.inv == 0.0f;               // NaN block or flushed block
+    if (a.scales) {
+        if (a.transposed) a.scales[(p * a.post + j) * a.nblk + b] = (uint8_t)bs.E;
+        else a.scales[t] = (uint8_t)bs.E;
+    }
+    const int64_t padded = a.nblk * a.block;
+    for (int64_t k = k0; k < k0 + a.block; ++k) {
+        if (k >= k1) {                              // padding of a ragged transposed block
+            if (a.codes && a.transposed) a.codes[(p * a.post + j) * padded + k] = 0;
+            continue;
+        }
+        const int64_t idx = base + k * a.post;
+        const float x = load1<DT>(a.in, idx);
+        const float v = dead ? 0.0f : x * bs.inv;   // exact: power-of-two scaling
+        float q = round_generic(v, a.fmt.mbits, a.fmt.ebits, a.fmt.max_norm, a.mode, true, true,
+                                a.noise ? a.noise[idx] : 0.f);
+        // keep the sign of x on results that rounded to zero
+        q = __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+        if (a.out) store1<DT>(a.out, idx, q * bs.scale);
+        if (a.codes) {
+            const uint8_t c = (uint8_t)encode1(q, a.fmt.ebits, a.fmt.mbits);
+            if (a.transposed) a.codes[(p * a.post + j) * padded + k] = c;
+            else a.codes[idx] = c;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dispatch
+// ---------------------------------------------------------------------------
+template <int DT, int MODE>
+static int launch_last(const MxArgs& a, int64_t nvec, int lanes, cudaStream_t st) {
+    const int64_t tile = (int64_t)kLastThreads * kLastUnroll;
+    const int64_t need = (nvec + tile - 1) / tile;
+    const int grid = (int)std::min<int64_t>(need, (int64_t)sm_count() * 16);
+    if (a.out && a.codes) mx_lastaxis_kernel<DT, MODE, true, true><<<grid, kLastThreads, 0, st>>>(a, nvec, lanes);
+    else if (a.codes) mx_lastaxis_kernel<DT, MODE, false, true><<<grid, kLastThreads, 0, st>>>(a, nvec, lanes);
+    else mx_lastaxis_kernel<DT, MODE, true, false><<<grid, kLastThreads, 0, st>>>(a, nvec, lanes);
+    return check_launch();
+}
+
+template <int DT, int MODE>
+static int launch_strided(const MxArgs& a, cudaStream_t st) {
+    constexpr int N = VecIO<DT, 8>::N;
+    const int64_t col_tiles = (a.post + (int64_t)kStrThreads * N - 1) / ((int64_t)kStrThreads * N);
+    const int64_t ntiles = col_tiles * a.pre * a.nblk;
+    const int grid = (int)std::min<int64_t>(ntiles, (int64_t)sm_count() * 64);
+    if (a.out && a.codes) mx_strided_kernel<DT, MODE, true, true><<<grid, kStrThreads, 0, st>>>(a, col_tiles, ntiles);
+    else if (a.codes) mx_strided_kernel<DT, MODE, false, true><<<grid, kStrThreads, 0, st>>>(a, col_tiles, ntiles);
+    else mx_strided_kernel<DT, MODE, true, false><<<grid, kStrThreads, 0, st>>>(a, col_tiles, ntiles);
+    return check_launch();
+}
+
+template <int DT>
+int dispatch_dt(const MxArgs& a, cudaStream_t st) {
+    constexpr int N16 = VecIO<DT, 16>::N;
+    constexpr int N8 = VecIO<DT, 8>::N;
+    const int64_t total = a.pre * a.axis_len * a.post;
+    const int P = a.fmt.mbits - 1;
+    const bool fast_math = a.mode <= RN_EVEN && P >= 1 && P <= 12 && a.fmt.ebits <= 5;
+    const bool pow2 = (a.block & (a.block - 1)) == 0;
+    const bool ptrs16 = aligned16(a.in) && (!a.out || aligned16(a.out)) && (!a.codes || aligned8(a.codes));
+    const bool ptrs8 = aligned8(a.in) && (!a.out || aligned8(a.out)) && (!a.codes || aligned8(a.codes));
+
+    if (fast_math && a.post == 1 && pow2 && a.block >= N16 && a.block <= 32 * N16 &&
+        a.axis_len % a.block == 0 && ptrs16 && !a.transposed) {
+        const int lanes = a.block / N16;
+        const int64_t nvec = total / N16;
+        switch (a.mode) {
+            case RN_AWAY: return launch_last<DT, RN_AWAY>(a, nvec, lanes, st);
+            case RZ:      return launch_last<DT, RZ>(a, nvec, lanes, st);
+            default:      return launch_last<DT, RN_EVEN>(a, nvec, lanes, st);
+        }
+    }
+    if (fast_math && a.post > 1 && a.block <= kMaxRows && a.post % N8 == 0 && ptrs8) {
+        switch (a.mode) {
+            case RN_AWAY: return launch_strided<DT, RN_AWAY>(a, st);
+            case RZ:      return launch_strided<DT, RZ>(a, st);
+            default:      return launch_strided<DT, RN_EVEN>(a, st);
+        }
+    }
+    const int64_t ntiles = a.pre * a.nblk * a.post;
+    const int threads = 128;
+    const int64_t grid = (ntiles + threads - 1) / threads;
+    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+    mx_generic_kernel<DT><<<(unsigned)grid, threads, 0, st>>>(a, ntiles);
+    return check_launch();
+}
+
+}  // namespace mxq

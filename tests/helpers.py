@@ -45,3 +45,34 @@ def bf16_bits(x):
 
 def bf16_vals(u16):
     return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def decode_container(codes, ebits, mbits):
+    """Element codes as libmxq writes them -> float64 values (before scaling):
+    e5m2 container for ebits == 5, e4m3 container for other float formats,
+    two's complement with (mbits-2) fraction bits for fixed point."""
+    c = codes.astype(np.int64)
+    if ebits == 0:
+        v = c & ((1 << mbits) - 1)
+        v = np.where(v >= (1 << (mbits - 1)), v - (1 << mbits), v)
+        return v / float(1 << (mbits - 2))
+    E, M = (5, 2) if ebits == 5 else (4, 3)
+    bias = (1 << (E - 1)) - 1
+    s = np.where((c >> (E + M)) & 1, -1.0, 1.0)
+    ef = (c >> M) & ((1 << E) - 1)
+    m = c & ((1 << M) - 1)
+    mag = np.where(ef == 0, np.ldexp(m.astype(np.float64), 1 - bias - M),
+                   np.ldexp((m | (1 << M)).astype(np.float64), ef - bias - M))
+    return s * mag
+
+
+def dequant_packed(codes, scales, block, axis, ebits, mbits):
+    """codes [.., n, ..] and E8M0 scales [.., nblk, ..] -> float32 values (NaN
+    where the scale byte is 255)."""
+    v = decode_container(codes, ebits, mbits)
+    n = codes.shape[axis]
+    se = np.repeat(scales.astype(np.int64), block, axis=axis)
+    se = np.take(se, np.arange(n), axis=axis)
+    out = np.ldexp(v, (se - 127).astype(np.int64))
+    out = np.where(se == 255, np.nan, out)
+    return out.astype(np.float32)
