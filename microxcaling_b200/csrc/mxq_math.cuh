@@ -22,6 +22,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <string.h>
+#include <math.h>
 
 namespace mxq {
 
@@ -37,6 +39,7 @@ struct ElemFmt {
     uint32_t emin_field;   // (emin + 127) << 23, emin = smallest normal exponent
     uint32_t k_field;      // exponent-field offset of the rounding constant
     float    max_norm;     // largest magnitude of the format
+    float    smul;         // 2^(k_field >> 23)
     int      ebits;        // 0 = fixed-point "int" format
     int      mbits;        // sign + significand bits (implicit one included)
     int      emax_elem;    // unbiased exponent of max_norm
@@ -50,6 +53,7 @@ __host__ inline ElemFmt make_fmt(int ebits, int mbits, float max_norm, int mode)
     f.emin_field = (uint32_t)(fmt_emin(ebits) + 127) << 23;
     f.k_field = (uint32_t)((mode == RN_AWAY ? 23 : 24) - P) << 23;
     f.max_norm = max_norm;
+    f.smul = ldexpf(1.0f, (mode == RN_AWAY ? 23 : 24) - P);
     f.ebits = ebits;
     f.mbits = mbits;
     uint32_t u;
@@ -80,6 +84,32 @@ __device__ __forceinline__ float round_grid_abs(uint32_t a, const uint32_t emin_
         r = __uint_as_float(t) - c;
     }
     return fminf(r, max_norm);
+}
+
+// The same rounding applied directly to an unscaled magnitude ax = |x|: the
+// grid is the element format's grid multiplied by the block scale, so the
+// smallest-normal constant `cmin` = 2^(emin + s) * scale and the saturation
+// bound are per-block values and no multiply into or out of the scaled domain
+// is needed.  `smul` = 2^s with s = 23-P (half-away) or 24-P (other modes).
+// The rounding constant only has to lie in the right binade and be an even
+// multiple of the grid spacing; for sources with at most 11 significand bits
+// (bf16, fp16) ax * 2^s qualifies, which moves its computation from the
+// integer pipe to the FMA pipe.  Returns the rounded, unsaturated magnitude.
+// Valid when cmin and ax * 2^s are normal finite floats (the caller checks the
+// block's exponent range and otherwise uses the scaled-domain routine above).
+template <int MODE, bool NARROW_SRC>
+__device__ __forceinline__ float round_unscaled_abs(float ax, const float cmin, const float smul,
+                                                    const uint32_t k_field) {
+    float c;
+    if (MODE != RN_EVEN && NARROW_SRC)
+        c = fmaxf(ax * smul, cmin);
+    else
+        c = __uint_as_float(max((__float_as_uint(ax) & 0x7f800000u) + k_field, __float_as_uint(cmin)));
+    if (MODE == RN_EVEN) return __fadd_rn(ax, c) - c;
+    if (MODE == RZ) return __fadd_rz(ax, c) - c;
+    uint32_t t = __float_as_uint(__fadd_rz(ax, c));
+    t = (t + 1u) & ~1u;
+    return __uint_as_float(t) - c;
 }
 
 // Biased exponent (0..255) of the block scale from the bits of the block's

@@ -65,6 +65,30 @@ __device__ __forceinline__ float quant_abs(uint32_t xb, const BlockScale& s, con
     return round_grid_abs<MODE>(__float_as_uint(v), f.emin_field, f.k_field, f.max_norm);
 }
 
+// Per-block constants of the unscaled fast path (see round_unscaled_abs).
+struct FastBlock {
+    float cmin;      // 2^(emin + s) * scale
+    float maxn;      // max_norm * scale
+    bool ok;         // the block's exponents allow the fast path
+    int E;           // biased scale exponent (E8M0 byte)
+};
+
+__device__ __forceinline__ FastBlock fast_block(uint32_t amax_bits, const MxArgs& a) {
+    FastBlock f;
+    const int Eraw = (int)(amax_bits >> 23);
+    const int E = scale_exp_from_absmax(amax_bits, a.fmt.emax_elem, a.scale_emax);
+    const int emin_biased = (int)(a.fmt.emin_field >> 23);           // emin + 127
+    const bool zero = amax_bits == 0;
+    // cmin's exponent field (emin + E + s) and x * 2^s must stay normal and
+    // finite; NaN and flushed blocks take the scaled-domain routine.
+    f.ok = zero || (E != 255 && E + emin_biased - 127 >= 1 && Eraw <= 228 && Eraw >= 1);
+    const int Ec = zero ? 127 : E;
+    f.cmin = __uint_as_float(a.fmt.emin_field + a.fmt.k_field + ((uint32_t)(Ec - 127) << 23));
+    f.maxn = __uint_as_float(__float_as_uint(a.fmt.max_norm) + ((uint32_t)(Ec - 127) << 23));
+    f.E = E;
+    return f;
+}
+
 __device__ __forceinline__ uint32_t pack_codes4(const float* q, const uint32_t* xb, const ElemFmt& f) {
     // four signed scaled values -> four code bytes (little endian)
     float s[4];
@@ -244,6 +268,233 @@ mx_strided_kernel(const MxArgs a, const int64_t col_tiles, const int64_t ntiles)
 }
 
 // ---------------------------------------------------------------------------
+// bf16 kernels: operate on packed pairs.  The block maximum is taken on the
+// packed 16-bit magnitudes (one AND and one two-lane max per two elements), the
+// results are bf16 values so their upper halves are packed back with one byte
+// permute, and saturation and sign are applied to the packed pair.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t vmax_u16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t vmin_u16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// two bf16 elements (word w) -> two dequantized bf16 elements, fast path.
+// lo/hi constants may differ (strided kernel: adjacent columns).
+template <int MODE>
+__device__ __forceinline__ uint32_t quant_pair_bf16(uint32_t w, float cmin_lo, float cmin_hi,
+                                                    uint32_t maxn_pair, const ElemFmt& f,
+                                                    float& r_lo, float& r_hi) {
+    const float xl = __uint_as_float(w << 16);
+    const float xh = __uint_as_float(w & 0xffff0000u);
+    r_lo = round_unscaled_abs<MODE, true>(fabsf(xl), cmin_lo, f.smul, f.k_field);
+    r_hi = round_unscaled_abs<MODE, true>(fabsf(xh), cmin_hi, f.smul, f.k_field);
+    uint32_t p = __byte_perm(__float_as_uint(r_lo), __float_as_uint(r_hi), 0x7632);
+    p = vmin_u16x2(p, maxn_pair);
+    return p | (w & 0x80008000u);
+}
+
+// scaled-domain fallback for one bf16 element held as fp32 bits
+template <int MODE>
+__device__ __forceinline__ uint32_t quant_slow_bits(uint32_t xb, const BlockScale& bs, const ElemFmt& f, float& q) {
+    q = quant_abs<MODE>(xb, bs, f);
+    return __float_as_uint(q * bs.scale) | (xb & 0x80000000u);
+}
+
+__device__ __forceinline__ uint32_t code_pair(float q_lo, float q_hi, uint32_t w, const ElemFmt& f) {
+    // signed scaled values -> two code bytes (lo element in bits 0..7)
+    const float sl = __uint_as_float(__float_as_uint(q_lo) | ((w << 16) & 0x80000000u));
+    const float sh = __uint_as_float(__float_as_uint(q_hi) | (w & 0x80000000u));
+    if (f.ebits == 0)
+        return (uint32_t)(__float2int_rn(ldexpf(sl, f.mbits - 2)) & 0xff) |
+               ((uint32_t)(__float2int_rn(ldexpf(sh, f.mbits - 2)) & 0xff) << 8);
+    return f.ebits == 5 ? encode2_e5m2(sl, sh) : encode2_e4m3(sl, sh);
+}
+
+constexpr int kLastBfThreads = 256;
+constexpr int kLastBfUnroll = 4;
+
+template <int MODE, bool WANT_DQ, bool WANT_CODES>
+__global__ void __launch_bounds__(kLastBfThreads)
+mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block) {
+    const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll);
+    uint4 raw[kLastBfUnroll];
+    bool live[kLastBfUnroll];
+#pragma unroll
+    for (int u = 0; u < kLastBfUnroll; ++u) {
+        const int64_t v = base + (int64_t)u * kLastBfThreads + threadIdx.x;
+        live[u] = v < nvec;
+        raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in) + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kLastBfUnroll; ++u) {
+        const int64_t v = base + (int64_t)u * kLastBfThreads + threadIdx.x;
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        uint32_t m2 = vmax_u16x2(vmax_u16x2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu),
+                                 vmax_u16x2(w[2] & 0x7fff7fffu, w[3] & 0x7fff7fffu));
+        uint32_t m = max(m2 & 0xffffu, m2 >> 16);
+        for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+        const uint32_t amax = m << 16;
+        const FastBlock fb = fast_block(amax, a);
+        uint32_t o[4];
+        float q[8];
+        if (fb.ok) {
+            const uint32_t mp = (__float_as_uint(fb.maxn) >> 16) * 0x10001u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] = quant_pair_bf16<MODE>(w[i], fb.cmin, fb.cmin, mp, a.fmt, q[2 * i], q[2 * i + 1]);
+            if (WANT_CODES) {
+                const float inv = inv_pow2_from_field(amax == 0 ? 127 : fb.E);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q[i] = fminf(q[i], fb.maxn) * inv;
+            }
+        } else {
+            const BlockScale bs = block_scale(amax, a);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t lo = quant_slow_bits<MODE>(w[i] << 16, bs, a.fmt, q[2 * i]);
+                const uint32_t hi = quant_slow_bits<MODE>(w[i] & 0xffff0000u, bs, a.fmt, q[2 * i + 1]);
+                o[i] = __byte_perm(lo, hi, 0x7632);
+            }
+        }
+        if (!live[u]) continue;
+        if (WANT_DQ) reinterpret_cast<uint4*>(a.out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (WANT_CODES) {
+            uint32_t c[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                c[i] = code_pair(q[4 * i], q[4 * i + 1], w[2 * i], a.fmt) |
+                       (code_pair(q[4 * i + 2], q[4 * i + 3], w[2 * i + 1], a.fmt) << 16);
+            reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
+            if ((threadIdx.x & (lanes_per_block - 1)) == 0) a.scales[v / lanes_per_block] = (uint8_t)fb.E;
+        }
+    }
+}
+
+constexpr int kStrBfThreads = 128;
+
+template <int MODE, bool WANT_DQ, bool WANT_CODES>
+__global__ void __launch_bounds__(kStrBfThreads)
+mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles) {
+    const int64_t t = blockIdx.x;
+    const int64_t ct = t % col_tiles;
+    const int64_t pb = t / col_tiles;
+    const int64_t b = pb % a.nblk;
+    const int64_t p = pb / a.nblk;
+    const int64_t col = ct * (kStrBfThreads * 4) + (int64_t)threadIdx.x * 4;
+    if (col >= a.post) return;
+    const int64_t row0 = b * a.block;
+    const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
+    const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
+    const uint16_t* in = reinterpret_cast<const uint16_t*>(a.in);
+    uint2 raw[kMaxRows];
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r)
+        raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
+    uint32_t m0 = 0, m1 = 0;
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+        m0 = vmax_u16x2(m0, raw[r].x & 0x7fff7fffu);
+        m1 = vmax_u16x2(m1, raw[r].y & 0x7fff7fffu);
+    }
+    const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
+    FastBlock fb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
+    const bool ok = fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
+    if (WANT_CODES) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (a.transposed) a.scales[(p * a.post + col + i) * a.nblk + b] = (uint8_t)fb[i].E;
+            else a.scales[(p * a.nblk + b) * a.post + col + i] = (uint8_t)fb[i].E;
+        }
+    }
+    uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+    uint32_t tc[4][kMaxRows / 4];          // transposed codes: [column][4 rows per word]
+    if (ok) {
+        const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
+        const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
+        float inv[4];
+        if (WANT_CODES) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) inv[i] = inv_pow2_from_field(amax[i] == 0 ? 127 : fb[i].E);
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) {
+            float q[4];
+            const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
+            const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
+            if (WANT_DQ && r < rows)
+                *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
+            if (WANT_CODES) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[i] = fminf(q[i], fb[i].maxn) * inv[i];
+                const uint32_t c01 = code_pair(q[0], q[1], raw[r].x, a.fmt);
+                const uint32_t c23 = code_pair(q[2], q[3], raw[r].y, a.fmt);
+                if (a.transposed) {
+                    const int sh = 8 * (r & 3);
+                    if ((r & 3) == 0) { tc[0][r >> 2] = 0; tc[1][r >> 2] = 0; tc[2][r >> 2] = 0; tc[3][r >> 2] = 0; }
+                    tc[0][r >> 2] |= (c01 & 0xffu) << sh;
+                    tc[1][r >> 2] |= (c01 >> 8) << sh;
+                    tc[2][r >> 2] |= (c23 & 0xffu) << sh;
+                    tc[3][r >> 2] |= (c23 >> 8) << sh;
+                } else if (r < rows) {
+                    *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01 | (c23 << 16);
+                }
+            }
+        }
+    } else {
+        BlockScale bs[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bs[i] = block_scale(amax[i], a);
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) {
+            float q[4];
+            const uint32_t l0 = quant_slow_bits<MODE>(raw[r].x << 16, bs[0], a.fmt, q[0]);
+            const uint32_t h0 = quant_slow_bits<MODE>(raw[r].x & 0xffff0000u, bs[1], a.fmt, q[1]);
+            const uint32_t l1 = quant_slow_bits<MODE>(raw[r].y << 16, bs[2], a.fmt, q[2]);
+            const uint32_t h1 = quant_slow_bits<MODE>(raw[r].y & 0xffff0000u, bs[3], a.fmt, q[3]);
+            if (WANT_DQ && r < rows)
+                *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) =
+                    make_uint2(__byte_perm(l0, h0, 0x7632), __byte_perm(l1, h1, 0x7632));
+            if (WANT_CODES) {
+                const uint32_t c01 = code_pair(q[0], q[1], raw[r].x, a.fmt);
+                const uint32_t c23 = code_pair(q[2], q[3], raw[r].y, a.fmt);
+                if (a.transposed) {
+                    const int sh = 8 * (r & 3);
+                    if ((r & 3) == 0) { tc[0][r >> 2] = 0; tc[1][r >> 2] = 0; tc[2][r >> 2] = 0; tc[3][r >> 2] = 0; }
+                    tc[0][r >> 2] |= (c01 & 0xffu) << sh;
+                    tc[1][r >> 2] |= (c01 >> 8) << sh;
+                    tc[2][r >> 2] |= (c23 & 0xffu) << sh;
+                    tc[3][r >> 2] |= (c23 >> 8) << sh;
+                } else if (r < rows) {
+                    *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01 | (c23 << 16);
+                }
+            }
+        }
+    }
+    if (WANT_CODES && a.transposed) {
+        const int64_t padded = a.nblk * a.block;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint8_t* dst = a.codes + (p * a.post + col + i) * padded + row0;
+            if (a.block == kMaxRows) {
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(tc[i][4], tc[i][5], tc[i][6], tc[i][7]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r)
+                    if (r < a.block) dst[r] = (uint8_t)(tc[i][r >> 2] >> (8 * (r & 3)));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // generic kernel: one thread per block of the tensor
 // ---------------------------------------------------------------------------
 template <int DT>
@@ -313,6 +564,28 @@ static int launch_strided(const MxArgs& a, cudaStream_t st) {
     return check_launch();
 }
 
+template <int MODE>
+static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream_t st) {
+    const int64_t tile = (int64_t)kLastBfThreads * kLastBfUnroll;
+    const int64_t grid = (nvec + tile - 1) / tile;
+    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+    if (a.out && a.codes) mx_lastaxis_bf16_kernel<MODE, true, true><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else if (a.codes) mx_lastaxis_bf16_kernel<MODE, false, true><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else mx_lastaxis_bf16_kernel<MODE, true, false><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    return check_launch();
+}
+
+template <int MODE>
+static int launch_strided_bf16(const MxArgs& a, cudaStream_t st) {
+    const int64_t col_tiles = (a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
+    const int64_t grid = col_tiles * a.pre * a.nblk;
+    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+    if (a.out && a.codes) mx_strided_bf16_kernel<MODE, true, true><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
+    else if (a.codes) mx_strided_bf16_kernel<MODE, false, true><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
+    else mx_strided_bf16_kernel<MODE, true, false><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
+    return check_launch();
+}
+
 template <int DT>
 int dispatch_dt(const MxArgs& a, cudaStream_t st) {
     constexpr int N16 = VecIO<DT, 16>::N;
@@ -328,6 +601,13 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
         a.axis_len % a.block == 0 && ptrs16 && !a.transposed) {
         const int lanes = a.block / N16;
         const int64_t nvec = total / N16;
+        if (DT == DT_BF16 && P <= 8) {
+            switch (a.mode) {
+                case RN_AWAY: return launch_last_bf16<RN_AWAY>(a, nvec, lanes, st);
+                case RZ:      return launch_last_bf16<RZ>(a, nvec, lanes, st);
+                default:      return launch_last_bf16<RN_EVEN>(a, nvec, lanes, st);
+            }
+        }
         switch (a.mode) {
             case RN_AWAY: return launch_last<DT, RN_AWAY>(a, nvec, lanes, st);
             case RZ:      return launch_last<DT, RZ>(a, nvec, lanes, st);
@@ -335,6 +615,13 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
         }
     }
     if (fast_math && a.post > 1 && a.block <= kMaxRows && a.post % N8 == 0 && ptrs8) {
+        if (DT == DT_BF16 && P <= 8 && (!a.codes || !a.transposed || aligned16(a.codes))) {
+            switch (a.mode) {
+                case RN_AWAY: return launch_strided_bf16<RN_AWAY>(a, st);
+                case RZ:      return launch_strided_bf16<RZ>(a, st);
+                default:      return launch_strided_bf16<RN_EVEN>(a, st);
+            }
+        }
         switch (a.mode) {
             case RN_AWAY: return launch_strided<DT, RN_AWAY>(a, st);
             case RZ:      return launch_strided<DT, RZ>(a, st);
