@@ -1,0 +1,123 @@
+"""MX block quantization.
+
+Drop-in for the reference's mx/mx_ops.py: `quantize_mx_op` (:301) and the
+internal `_quantize_mx` (:173).  CUDA tensors go to the sm_100a kernels through
+the C ABI whatever `custom_cuda` says (one axis: a single kernel launch; several
+axes: not supported by the kernels, handled on the exact host formulation after
+a copy is refused -- see below).  CPU tensors use an exact float64 formulation.
+"""
+import torch
+
+from .formats import ElemFormat, _get_format_params
+from .specs import mx_assert_test
+
+_MODE = {"nearest": 0, "floor": 1, "even": 2, "dither": 3}
+
+
+def _host_mx(A, scale_bits, ebits, mbits, max_norm, axes, block_size, round, flush, noise=None):
+    """Exact torch formulation for CPU tensors, any number of shared axes."""
+    from .elemwise_ops import _round_host
+    x = A.detach().to(torch.float64)
+    nd = x.dim()
+    axes = sorted(a % nd for a in axes)
+    # view each shared axis as (blocks, block), zero-padding a ragged tail
+    shape, pads = [], []
+    for d in range(nd):
+        n = x.shape[d]
+        if d in axes:
+            b = block_size if 0 < block_size < n else n
+            nb = (n + b - 1) // b if n else 0
+            pads.append(nb * b - n)
+            shape += [nb, b]
+        else:
+            pads.append(0)
+            shape.append(n)
+    if any(pads):
+        pad = []
+        for p in reversed(pads):
+            pad += [0, p]
+        x = torch.nn.functional.pad(x, pad)
+    xb = x.reshape(shape)
+    red, k = [], 0
+    for d in range(nd):
+        if d in axes:
+            red.append(k + 1)
+            k += 2
+        else:
+            k += 1
+    a = xb.abs()
+    amax = torch.amax(torch.where(torch.isnan(a), torch.full_like(a, float("inf")), a), dim=red, keepdim=True)
+    amax32 = amax.to(torch.float32)
+    E = (amax32.view(torch.int32) >> 23) & 0xFF                  # biased exponent of the maximum
+    _, emax_elem = torch.frexp(torch.tensor(float(max_norm)))
+    emax_elem = int(emax_elem) - 1
+    smax = (1 << (scale_bits - 1)) - 1
+    nan_blk = E == 255
+    Es = E - emax_elem
+    nan_blk = nan_blk | ((Es - 127) > smax)
+    Es = torch.where((Es - 127) < -smax, torch.full_like(Es, 127 - smax), Es)
+    dead = (E == 0) if flush else torch.zeros_like(nan_blk)
+    se = (Es - 127).to(torch.int32)
+    v = torch.ldexp(xb, (-se).expand_as(xb))
+    v = torch.where(dead.expand_as(v), torch.zeros_like(v), v)
+    v = torch.where(torch.isfinite(v), v, torch.zeros_like(v))
+    nz = None
+    if noise is not None:
+        nz = noise.to(torch.float32)
+        if any(pads):
+            nz = torch.nn.functional.pad(nz, pad)
+        nz = nz.reshape(shape)
+    q = _round_host(v, mbits, ebits, max_norm, round, True, True, nz)
+    y = torch.ldexp(q, se.expand_as(q))
+    y = torch.where(nan_blk.expand_as(y), torch.full_like(y, float("nan")), y)
+    y = y.reshape(x.shape)
+    if any(pads):
+        y = y[tuple(slice(0, n) for n in A.shape)]
+    return y.to(A.dtype)
+
+
+def _quantize_mx(A, scale_bits, elem_format, shared_exp_method="max", axes=None, block_size=0,
+                 round="nearest", flush_fp32_subnorms=False, custom_cuda=False, noise=None):
+    """MX fake-quantization: blocks of `block_size` elements along each axis of
+    `axes` share a power-of-two scale of `scale_bits` bits."""
+    if elem_format is None:
+        return A
+    assert scale_bits > 0
+    if axes is None:
+        raise Exception("axes required in order to determine which dimension to apply block size to")
+    axes = [axes] if type(axes) == int else list(axes)
+    axes = [x + A.ndim if x < 0 else x for x in axes]
+    if shared_exp_method != "max":
+        raise Exception("Unrecognized shared exponent selection method %s" % (shared_exp_method))
+    if round not in _MODE:
+        raise Exception("Unrecognized round method %s" % (round))
+    ebits, mbits, _, max_norm, _ = _get_format_params(elem_format)
+    if A.is_cuda:
+        if len(axes) != 1:
+            raise NotImplementedError("MX quantization over several shared axes is not supported on CUDA tensors")
+        from . import _backend
+        if round == "dither" and noise is None:
+            noise = torch.rand_like(A, dtype=torch.float32)
+        return _backend.quantize_mx(A.contiguous(), scale_bits, ebits, mbits, max_norm, block_size, axes[0],
+                                    flush_fp32_subnorms, _MODE[round],
+                                    noise.contiguous() if noise is not None else None)
+    if A.numel() == 0:
+        return A.clone()
+    return _host_mx(A, scale_bits, ebits, mbits, max_norm, axes, block_size, round, flush_fp32_subnorms, noise)
+
+
+def quantize_mx_op(A, mx_specs: dict, elem_format=None, block_size=None, axes=None, round="nearest",
+                   expand_and_reshape=False):
+    """Quantize A to the MX format `elem_format` along `axes` per mx_specs."""
+    mx_assert_test(mx_specs)
+    if elem_format is None:
+        return A
+    if type(elem_format) is str:
+        elem_format = ElemFormat.from_str(elem_format)
+    if block_size is None:
+        block_size = mx_specs["block_size"]
+    scale_bits = 8 if mx_specs["scale_bits"] == 0 else mx_specs["scale_bits"]
+    return _quantize_mx(A, scale_bits, elem_format, block_size=block_size, axes=axes, round=round,
+                        shared_exp_method=mx_specs["shared_exp_method"],
+                        flush_fp32_subnorms=mx_specs["mx_flush_fp32_subnorms"],
+                        custom_cuda=mx_specs["custom_cuda"])
