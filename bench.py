@@ -188,7 +188,7 @@ def main():
             eb, mb, _, mn, _ = fmt_params[MX_FORMATS[i // 2]]
             pre, n, post = (1, ROWS, COLS) if i % 2 == 0 else (ROWS, COLS, 1)
             rc = L.mxq_quantize_mx(x.data_ptr(), y.data_ptr(), None, None, be.BF16, pre, n, post, 32, 8,
-                                   eb, mb, mn, 0, 0, None, 0, sp)
+                                   eb, mb, mn, 0, 0, None, 0, 0, sp)
         else:
             rc = L.mxq_quantize_elemwise(x.data_ptr(), y.data_ptr(), be.BF16, be.BF16, x.numel(), 9, 8,
                                          BF16_MAX_NORM, 2, 0, 1, None, sp)

@@ -46,6 +46,7 @@ extern "C" {
 
 /* flags of mxq_quantize_mx */
 #define MXQ_CODES_TRANSPOSED 1   /* write codes/scales with the blocked axis innermost */
+#define MXQ_SCALES_GEMM_LAYOUT 2  /* write scales in the chunk layout mxq_gemm_mx reads (block must be 32) */
 
 const char* mxq_status_string(int status);
 int mxq_version(void);
@@ -75,12 +76,22 @@ int mxq_version(void);
  *   rmode     as in the reference signature
  *   noise     fp32 uniform [0,1) tensor of the input's shape for
  *             MXQ_ROUND_DITHER, else NULL
+ *   flags     MXQ_CODES_TRANSPOSED, MXQ_SCALES_GEMM_LAYOUT
+ *   sf_rows_per_batch  only with MXQ_SCALES_GEMM_LAYOUT: the operand is seen as
+ *             [batch, rows, K] with K the blocked axis.  Not transposed
+ *             (post == 1): the pre axis is batch * rows and this gives rows
+ *             (0: one batch).  Transposed: batch = pre, rows = post.  The scale
+ *             of (batch b, row r, block k) is byte
+ *               ((b*ceil(rows/128) + r/128) * ceil(nblocks/4) + k/4) * 512
+ *                 + (r%32)*16 + ((r%128)/32)*4 + k%4
+ *             of the scales buffer (mxq_sf_bytes gives its size); bytes of
+ *             padding rows / blocks are not written.
  */
 int mxq_quantize_mx(const void* in, void* out, void* codes, void* scales, int dtype,
                     int64_t pre, int64_t axis_len, int64_t post, int block,
                     int scale_bits, int elem_ebits, int elem_mbits, float elem_max_norm,
                     int flush_fp32_subnorms, int rmode, const void* noise, int flags,
-                    void* stream);
+                    int64_t sf_rows_per_batch, void* stream);
 
 /*
  * Elementwise rounding to a (bits, exp_bits) format.  Replaces
@@ -101,6 +112,39 @@ int mxq_quantize_elemwise(const void* in, void* out, int in_dtype, int out_dtype
  */
 int mxq_reduce_sum_inner(const void* in, void* out, int64_t rows, int64_t inner, void* stream);
 int mxq_reduce_max_inner(const void* in, void* out, int64_t rows, int64_t inner, void* stream);
+
+/*
+ * Block-scaled MX GEMM on the tensor cores (tcgen05 kind::mxf8f6f4):
+ *   C[b] = A[b] (M x K) * B[b]^T (N x K),  b < batch, fp32 accumulation.
+ * Takes the place of the library GEMM the reference runs on dequantized
+ * operands: F.linear / torch.matmul / torch.bmm in mx/linear.py:86,147,179,
+ * mx/matmul.py:86,167,172 and mx/bmm.py:59,116,121, together with the
+ * quantize_elemwise_op that follows it (mx/linear.py:88-96).
+ *   a_codes [batch, M, K], b_codes [batch, N, K]   element codes from
+ *             mxq_quantize_mx (K contiguous)
+ *   a_scales, b_scales   E8M0 scales in the MXQ_SCALES_GEMM_LAYOUT layout
+ *   a_fmt, b_fmt         code container: 0 = e4m3, 1 = e5m2
+ *   c         [batch, M, N], out_dtype MXQ_F32 or MXQ_BF16
+ *   out_bfloat_bits, out_round   bfloat rounding of the result (mx_specs
+ *             'bfloat' and 'round_output'); 0 or 32 bits, or round -1: none
+ *   bias      fp32 [N] or NULL: c = round(round(acc) + bias)
+ *   tile_n    0 (automatic), 128 or 256
+ * K must be a multiple of 128; pointers 16-byte aligned.  The first call on a
+ * device allocates a 4-byte status word with cudaMalloc (kept until exit); a
+ * kernel that gives up on a wait stores MXQ_ERR_DEVICE there, see
+ * mxq_device_status.
+ */
+int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
+                int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
+                void* stream);
+
+/* Bytes of a scales buffer in the GEMM layout for a [batch, rows, K] operand. */
+int64_t mxq_sf_bytes(int64_t batch, int64_t rows, int64_t K);
+
+/* Synchronously reads (and optionally clears) the current device's status word:
+ * 0, or MXQ_ERR_DEVICE after a kernel timed out on a wait. */
+int mxq_device_status(int clear);
 
 #ifdef __cplusplus
 }

@@ -21,6 +21,7 @@ F32, F16, BF16 = 0, 1, 2
 _DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 ROUND_DITHER = 3
 CODES_TRANSPOSED = 1
+SCALES_GEMM_LAYOUT = 2
 
 
 class MxqError(RuntimeError):
@@ -38,7 +39,11 @@ def lib():
         L.mxq_status_string.restype = ctypes.c_char_p
         L.mxq_status_string.argtypes = [i32]
         L.mxq_quantize_mx.argtypes = [vp, vp, vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32,
-                                      i32, i32, vp, i32, vp]
+                                      i32, i32, vp, i32, i64, vp]
+        L.mxq_gemm_mx.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp, i32, vp]
+        L.mxq_sf_bytes.argtypes = [i64, i64, i64]
+        L.mxq_sf_bytes.restype = i64
+        L.mxq_device_status.argtypes = [i32]
         L.mxq_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, vp]
         L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
@@ -79,7 +84,8 @@ def _split(shape, axis):
 
 
 def quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False, rmode=0,
-                noise=None, want_dq=True, want_codes=False, transposed=False):
+                noise=None, want_dq=True, want_codes=False, transposed=False, gemm_layout=False,
+                rows_per_batch=0):
     """MX-quantize CUDA tensor A in blocks of `block` along `axis`.
 
     Returns the dequantized tensor (A's dtype), or with want_codes a tuple
@@ -101,6 +107,14 @@ def quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False,
         else:
             codes = torch.empty(shape, dtype=torch.uint8, device=A.device)
             scales = torch.empty(shape[:axis] + [nblk] + shape[axis + 1:], dtype=torch.uint8, device=A.device)
+        if gemm_layout:
+            # [batch, rows, K] operand: 512-byte chunks per 128 rows x 128 K, padding defined as zero
+            if transposed:
+                nb, rows = pre, post
+            else:
+                rows = rows_per_batch if rows_per_batch else pre
+                nb = pre // rows if rows else 0
+            scales = torch.zeros(lib().mxq_sf_bytes(nb, rows, nblk * blk), dtype=torch.uint8, device=A.device)
     if noise is not None:
         _require_cuda(noise, "noise")
         assert noise.dtype == torch.float32 and noise.shape == A.shape
@@ -108,7 +122,8 @@ def quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False,
         check(lib().mxq_quantize_mx(_ptr(A), _ptr(out), _ptr(codes), _ptr(scales), _DT[A.dtype],
                                     pre, n, post, blk, int(scale_bits), int(ebits), int(mbits),
                                     float(max_norm), int(bool(flush)), int(rmode), _ptr(noise),
-                                    CODES_TRANSPOSED if transposed else 0, _stream(A)))
+                                    (CODES_TRANSPOSED if transposed else 0) | (SCALES_GEMM_LAYOUT if gemm_layout else 0),
+                                    int(rows_per_batch), _stream(A)))
     if want_codes:
         return out, codes, scales
     return out
@@ -129,6 +144,28 @@ def quantize_elemwise(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=Fal
                                           int(bool(saturate_normals)), int(bool(allow_denorm)),
                                           _ptr(noise), _stream(A)))
     return out
+
+
+def gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, M, N, K, a_fmt=0, b_fmt=0,
+            out_dtype=torch.bfloat16, bfloat_bits=16, round_mode=0, bias=None, tile_n=0, out=None):
+    """C[b] = A[b] @ B[b]^T on the block-scaled tensor cores; see mxq_gemm_mx."""
+    for t in (a_codes, b_codes, a_scales, b_scales):
+        if not t.is_cuda or not t.is_contiguous() or t.dtype != torch.uint8:
+            raise MxqError("GEMM operands must be contiguous uint8 CUDA tensors")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=out_dtype, device=a_codes.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    with torch.cuda.device(a_codes.device):
+        check(lib().mxq_gemm_mx(_ptr(a_codes), _ptr(a_scales), _ptr(b_codes), _ptr(b_scales), _ptr(out),
+                                batch, M, N, K, a_fmt, b_fmt, _DT[out.dtype], int(bfloat_bits), int(round_mode),
+                                _ptr(bias), int(tile_n), _stream(a_codes)))
+    return out
+
+
+def device_status(clear=True):
+    """Synchronous read of the device status word (0 = no kernel gave up on a wait)."""
+    return lib().mxq_device_status(1 if clear else 0)
 
 
 def _reduce(A, fn):

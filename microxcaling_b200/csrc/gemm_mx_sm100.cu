@@ -1,0 +1,378 @@
+// Block-scaled MX GEMM for sm_100a:  C[b] = A[b] (M x K) * B[b]^T (N x K)
+//
+// Operands are the packed outputs of the MX quantizer: one fp8-container code
+// per element (K contiguous) and one E8M0 scale per 32 elements, the scales in
+// the 512-byte chunk layout tensor memory wants (see mxq_sf_offset in mxq.h).
+// The products are formed by tcgen05.mma kind::mxf8f6f4 with the block scales
+// applied by the tensor core, accumulated in fp32 in tensor memory -- this
+// replaces the reference's "dequantize, then fp32 / bf16 library GEMM"
+// (mx/linear.py:83-86, mx/matmul.py:83-86, mx/bmm.py:56-59).  The epilogue
+// applies the bfloat rounding of mx_specs (and the bias add with its second
+// rounding, mx/linear.py:88-96) while the accumulator is read out.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer: A and B tiles (128-byte swizzle) and the scale
+//               chunks into a STAGES-deep shared-memory ring
+//   warp 1      MMA issuer: copies the scales to tensor memory (tcgen05.cp),
+//               issues four K=32 MMAs per 128-wide K block, commits the stage
+//               back to the producer and finished accumulators to the epilogue
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one 32-lane quarter
+//               each), rounding, stores
+// Accumulators are double buffered in tensor memory so the epilogue of one
+// tile overlaps the main loop of the next.  All waits are bounded; on time-out
+// the kernel records a status word, drains and exits.
+#include <cuda.h>
+#include <algorithm>
+#include <cstring>
+#include "mxq_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace mxq {
+
+constexpr int kBM = 128;          // tile rows (MMA M)
+constexpr int kBK = 128;          // K bytes per stage = four MMA K steps
+constexpr int kGemmThreads = 192;
+constexpr int kSfChunk = 512;     // bytes of scales per 128 rows x 128 K
+
+struct GemmArgs {
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    void* c;
+    const void* bias;           // fp32 [N] or null
+    int* status;                // device status word
+    int64_t M, N, K, batch;
+    int64_t m_tiles, n_tiles, k_blocks;
+    int64_t sfa_rows128, sfb_rows128;   // 128-row chunks per batch element
+    uint32_t idesc;
+    int out_dtype;              // DT_F32 or DT_BF16
+    int round_mode;             // RN_AWAY / RZ / RN_EVEN, or -1: no rounding
+    uint32_t drop;              // low bits removed by the bfloat rounding
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int kA = kBM * kBK;
+    static constexpr int kB = BN * kBK;
+    static constexpr int kSFA = kSfChunk;
+    static constexpr int kSFB = (BN / 128) * kSfChunk;
+    static constexpr int kStage = kA + kB + kSFA + kSFB;
+    static constexpr int kBarOff = STAGES * kStage;
+    static constexpr int kTotal = kBarOff + 256 + 1024;   // barriers + alignment slack
+};
+
+// fp32 accumulator -> bfloat grid (integer rounding on the raw bits; formats
+// with eight exponent bits share fp32's exponent layout).
+__device__ __forceinline__ float round_out(float v, int mode, uint32_t drop) {
+    if (mode < 0) return v;
+    const uint32_t u = __float_as_uint(v);
+    const uint32_t mag = u & 0x7fffffffu;
+    if (mag >= kInf) return v;
+    const uint32_t mask = (1u << drop) - 1u;
+    uint32_t r = mag;
+    if (mode == RN_AWAY) r += 1u << (drop - 1);
+    else if (mode == RN_EVEN) r += (mask >> 1) + ((mag >> drop) & 1u);
+    r &= ~mask;
+    return __uint_as_float(r | (u & 0x80000000u));
+}
+
+template <int BN, int STAGES, int ACC_BUFS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmArgs g) {
+    using S = GemmSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
+    // barrier indices
+    uint64_t* full = bars;                       // [STAGES]
+    uint64_t* empty = bars + STAGES;             // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;      // [ACC_BUFS]
+    uint64_t* acc_empty = acc_full + ACC_BUFS;   // [ACC_BUFS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    constexpr uint32_t kAccCols = BN * ACC_BUFS;
+    constexpr uint32_t kSfaCol = kAccCols;
+    constexpr uint32_t kSfbCol = kAccCols + 4;
+    constexpr uint32_t kTmemCols = 512;
+    static_assert(kAccCols + 4 + BN / 32 <= kTmemCols, "tensor memory budget");
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
+        for (int b = 0; b < ACC_BUFS; ++b) { ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1); ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), 4); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t tiles_per_batch = g.m_tiles * g.n_tiles;
+    const int64_t total_tiles = tiles_per_batch * g.batch;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (ptx::elect_one()) {
+            ptx::prefetch_tmap(&tmap_a);
+            ptx::prefetch_tmap(&tmap_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int64_t bi = t / tiles_per_batch;
+                const int64_t r = t % tiles_per_batch;
+                const int64_t mt = r / g.n_tiles, nt = r % g.n_tiles;   // n fastest: neighbours share the A tile
+                for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (it >= (uint32_t)STAGES && !ptx::mbar_wait(ptx::smem_u32(&empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = smem + (size_t)s * S::kStage;
+                    const uint32_t bar = ptx::smem_u32(&full[s]);
+                    ptx::mbar_expect_tx(bar, S::kStage);
+                    ptx::tma_load_3d(ptx::smem_u32(st), &tmap_a, bar, (int)(kb * kBK), (int)(mt * kBM), (int)bi);
+                    ptx::tma_load_3d(ptx::smem_u32(st + S::kA), &tmap_b, bar, (int)(kb * kBK), (int)(nt * BN), (int)bi);
+                    ptx::bulk_load(ptx::smem_u32(st + S::kA + S::kB),
+                                   g.sfa + ((bi * g.sfa_rows128 + mt) * g.k_blocks + kb) * kSfChunk, kSfChunk, bar);
+#pragma unroll
+                    for (int j = 0; j < BN / 128; ++j)
+                        ptx::bulk_load(ptx::smem_u32(st + S::kA + S::kB + S::kSFA + j * kSfChunk),
+                                       g.sfb + ((bi * g.sfb_rows128 + nt * (BN / 128) + j) * g.k_blocks + kb) * kSfChunk,
+                                       kSfChunk, bar);
+                }
+            }
+            if (!ok) {
+                // drain: give copies already in flight a bounded time to land
+                for (int s = 0; s < STAGES; ++s)
+                    for (uint32_t i = 0; i < 4096 && !ptx::mbar_try_wait(ptx::smem_u32(&full[s]), 0) &&
+                                         !ptx::mbar_try_wait(ptx::smem_u32(&full[s]), 1); ++i) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (ptx::elect_one()) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+                const int buf = tile_i % ACC_BUFS;
+                const uint32_t acc_ph = (tile_i / ACC_BUFS) & 1;
+                if (tile_i >= (uint32_t)ACC_BUFS && !ptx::mbar_wait(ptx::smem_u32(&acc_empty[buf]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full[s]), ph, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    uint8_t* st = smem + (size_t)s * S::kStage;
+                    const uint32_t a_addr = ptx::smem_u32(st);
+                    const uint32_t b_addr = ptx::smem_u32(st + S::kA);
+                    const uint32_t sfa_addr = ptx::smem_u32(st + S::kA + S::kB);
+                    const uint32_t sfb_addr = sfa_addr + S::kSFA;
+                    // scales: 32 rows x 16 bytes per chunk, 8-row groups 128 bytes apart, no swizzle
+                    ptx::tc_cp_32x128b_warpx4(tmem_base + kSfaCol, ptx::smem_desc(sfa_addr, 0, 128, 0));
+#pragma unroll
+                    for (int j = 0; j < BN / 128; ++j)
+                        ptx::tc_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * j, ptx::smem_desc(sfb_addr + j * kSfChunk, 0, 128, 0));
+#pragma unroll
+                    for (int k = 0; k < kBK / 32; ++k) {
+                        // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; a K step of
+                        // 32 elements moves the start address by 32 bytes inside the swizzle atom
+                        const uint64_t ad = ptx::smem_desc(a_addr + 32 * k, 0, 1024, 2);
+                        const uint64_t bd = ptx::smem_desc(b_addr + 32 * k, 0, 1024, 2);
+                        const uint32_t id = g.idesc | ((uint32_t)k << 4) | ((uint32_t)k << 29);
+                        ptx::tc_mma_mxf8f6f4(d_tmem, ad, bd, id, (tmem_base + kSfaCol) | ((uint32_t)k << 30),
+                                             (tmem_base + kSfbCol) | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(ptx::smem_u32(&empty[s]));        // stage reusable once these MMAs retire
+                }
+                if (ok) ptx::tc_commit(ptx::smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;                               // the tensor-memory lane quarter this warp may read
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+            const int buf = tile_i % ACC_BUFS;
+            const uint32_t acc_ph = (tile_i / ACC_BUFS) & 1;
+            const int64_t bi = t / tiles_per_batch;
+            const int64_t r = t % tiles_per_batch;
+            const int64_t mt = r / g.n_tiles, nt = r % g.n_tiles;
+            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buf]), acc_ph, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const int64_t row = mt * kBM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_32x32b_x16(taddr + c0, v);
+                ptx::tmem_ld_wait();
+                const int64_t col = nt * BN + c0;
+                if (row < g.M && col < g.N) {
+                    float f[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        f[i] = round_out(__uint_as_float(v[i]), g.round_mode, g.drop);
+                        if (g.bias) f[i] = round_out(f[i] + reinterpret_cast<const float*>(g.bias)[min(col + i, g.N - 1)], g.round_mode, g.drop);
+                    }
+                    const int64_t off = (bi * g.M + row) * g.N + col;
+                    if (col + 16 <= g.N && (g.N % 8) == 0) {
+                        if (g.out_dtype == DT_F32) {
+                            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.c) + off);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) o[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                        } else {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.c) + off);
+                            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    } else {
+                        for (int i = 0; i < 16 && col + i < g.N; ++i) {
+                            if (g.out_dtype == DT_F32) reinterpret_cast<float*>(g.c)[off + i] = f[i];
+                            else reinterpret_cast<__nv_bfloat16*>(g.c)[off + i] = __float2bfloat16_rn(f[i]);
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(g.status, MXQ_ERR_DEVICE);
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [batch, rows, K] bytes, K contiguous; box = 128 bytes of K x box_rows rows
+static int make_operand_map(CUtensorMap* m, const void* base, int64_t batch, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MXQ_ERR_CUDA;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)(K * rows)};
+    cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
+}
+
+static int* device_status_word() {
+    // one status word per device, allocated on first use and kept until exit
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(words[dev], 0, sizeof(int));
+    }
+    return words[dev];
+}
+
+template <int BN, int STAGES, int ACC_BUFS>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t st) {
+    using S = GemmSmem<BN, STAGES>;
+    auto kern = gemm_mx_kernel<BN, STAGES, ACC_BUFS>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
+        return MXQ_ERR_CUDA;
+    const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, g);
+    return check_launch();
+}
+
+}  // namespace mxq
+
+extern "C" int64_t mxq_sf_bytes(int64_t batch, int64_t rows, int64_t K) {
+    if (batch < 0 || rows < 0 || K < 0) return -1;
+    return batch * ((rows + 127) / 128) * ((K + 127) / 128) * 512;
+}
+
+extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                           void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
+                           int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
+                           void* stream) {
+    using namespace mxq;
+    if (batch < 0 || M < 0 || N < 0 || K < 0) return MXQ_ERR_BAD_ARG;
+    if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
+    if (!a_codes || !a_scales || !b_codes || !b_scales || !c) return MXQ_ERR_BAD_ARG;
+    if (K == 0 || K % kBK != 0) return MXQ_ERR_UNSUPPORTED;            // K must be a multiple of 128
+    if (a_fmt < 0 || a_fmt > 1 || b_fmt < 0 || b_fmt > 1) return MXQ_ERR_BAD_ARG;
+    if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_BAD_ARG;
+    if (out_round < -1 || out_round > MXQ_ROUND_EVEN) return MXQ_ERR_BAD_ARG;
+    if (out_bfloat_bits != 0 && (out_bfloat_bits < 10 || out_bfloat_bits > 32)) return MXQ_ERR_BAD_ARG;
+    if (!aligned16(a_codes) || !aligned16(b_codes) || !aligned16(a_scales) || !aligned16(b_scales) || !aligned16(c))
+        return MXQ_ERR_ALIGN;
+    if (batch > 0x7fffffff || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return MXQ_ERR_TOO_LARGE;
+    int bn = (tile_n == 128 || tile_n == 256) ? tile_n : (N > 128 ? 256 : 128);
+    // a 256-wide tile reads two 128-row scale chunks per K block; fall back to 128-wide
+    // tiles when the scale buffer of B has an odd number of row chunks
+    if (bn == 256 && ((N + 127) / 128) % 2 != 0) bn = 128;
+    GemmArgs g;
+    g.sfa = (const uint8_t*)a_scales; g.sfb = (const uint8_t*)b_scales; g.c = c; g.bias = bias;
+    g.status = device_status_word();
+    if (!g.status) return MXQ_ERR_CUDA;
+    g.M = M; g.N = N; g.K = K; g.batch = batch;
+    g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = K / kBK;
+    g.sfa_rows128 = (M + 127) / 128; g.sfb_rows128 = (N + 127) / 128;
+    g.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, kBM, bn);
+    g.out_dtype = out_dtype;
+    const bool rounds = out_bfloat_bits >= 10 && out_bfloat_bits < 32 && out_round >= 0;
+    g.round_mode = rounds ? out_round : -1;
+    g.drop = rounds ? (uint32_t)(32 - out_bfloat_bits) : 0;
+    CUtensorMap ta, tb;
+    int rc = make_operand_map(&ta, a_codes, batch, M, K, kBM);
+    if (rc) return rc;
+    rc = make_operand_map(&tb, b_codes, batch, N, K, bn);
+    if (rc) return rc;
+    if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, g, (cudaStream_t)stream);
+    return launch_gemm<128, 6, 2>(ta, tb, g, (cudaStream_t)stream);
+}
+
+extern "C" int mxq_device_status(int clear) {
+    int* w = mxq::device_status_word();
+    if (!w) return MXQ_ERR_CUDA;
+    int v = 0;
+    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MXQ_ERR_CUDA;
+    if (clear && v != 0) cudaMemset(w, 0, sizeof(int));
+    return v;
+}

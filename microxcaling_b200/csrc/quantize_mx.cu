@@ -12,7 +12,7 @@ extern "C" int mxq_quantize_mx(const void* in, void* out, void* codes, void* sca
                                int64_t pre, int64_t axis_len, int64_t post, int block,
                                int scale_bits, int elem_ebits, int elem_mbits, float elem_max_norm,
                                int flush_fp32_subnorms, int rmode, const void* noise, int flags,
-                               void* stream) {
+                               int64_t sf_rows_per_batch, void* stream) {
     using namespace mxq;
     if (pre < 0 || axis_len < 0 || post < 0) return MXQ_ERR_BAD_ARG;
     if (pre == 0 || axis_len == 0 || post == 0) return MXQ_OK;        // empty tensor: nothing to do
@@ -36,6 +36,9 @@ extern "C" int mxq_quantize_mx(const void* in, void* out, void* codes, void* sca
     a.flush = flush_fp32_subnorms != 0;
     a.mode = rmode;
     a.transposed = (flags & MXQ_CODES_TRANSPOSED) != 0;
+    a.sf_gemm = (flags & MXQ_SCALES_GEMM_LAYOUT) != 0;
+    a.sf_rpb = sf_rows_per_batch > 0 ? sf_rows_per_batch : (a.transposed ? post : pre);
+    if (a.sf_gemm && (block != 32 || (!a.transposed && post != 1))) return MXQ_ERR_UNSUPPORTED;
     a.fmt = make_fmt(elem_ebits, elem_mbits, elem_max_norm, rmode);
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {

@@ -36,8 +36,22 @@ struct MxArgs {
     int flush;
     int mode;
     int transposed;
+    int sf_gemm;            // scales in the 512-byte chunk layout of the GEMM
+    int64_t sf_rpb;         // rows per batch element for that layout
     ElemFmt fmt;
 };
+
+// Byte index of the scale of block b of (pre index p, post index j).
+__device__ __forceinline__ int64_t scale_index(const MxArgs& a, int64_t p, int64_t b, int64_t j) {
+    if (a.sf_gemm) {
+        int64_t batch, row;
+        if (a.transposed) { batch = p; row = j; }
+        else { batch = p / a.sf_rpb; row = p % a.sf_rpb; }
+        const int64_t r128 = (a.sf_rpb + 127) >> 7, kb4 = (a.nblk + 3) >> 2;
+        return ((batch * r128 + (row >> 7)) * kb4 + (b >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (b & 3);
+    }
+    return a.transposed ? (p * a.post + j) * a.nblk + b : (p * a.nblk + b) * a.post + j;
+}
 
 // Per-block constants derived from the block's absolute maximum.
 struct BlockScale {
@@ -148,7 +162,10 @@ mx_lastaxis_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block
                 for (int i = 0; i < N / 4; ++i) c[i] = pack_codes4(&q[4 * i], &xb[u][4 * i], a.fmt);
                 if (N == 4) *reinterpret_cast<uint32_t*>(a.codes + v * N) = c[0];
                 else *reinterpret_cast<uint2*>(a.codes + v * N) = make_uint2(c[0], c[N / 4 - 1]);
-                if ((threadIdx.x & (lanes_per_block - 1)) == 0) a.scales[v / lanes_per_block] = (uint8_t)bs.E;
+                if ((threadIdx.x & (lanes_per_block - 1)) == 0) {
+                    const int64_t blk = v / lanes_per_block;
+                    a.scales[scale_index(a, blk / a.nblk, blk % a.nblk, 0)] = (uint8_t)bs.E;
+                }
             }
             if (WANT_DQ) {
                 uint32_t ob[N];
@@ -203,15 +220,9 @@ mx_strided_kernel(const MxArgs a, const int64_t col_tiles, const int64_t ntiles)
 #pragma unroll
         for (int i = 0; i < N; ++i) bs[i] = block_scale(m[i], a);
 
-        if (WANT_CODES && !a.transposed) {
+        if (WANT_CODES) {
 #pragma unroll
-            for (int i = 0; i < N; ++i)
-                a.scales[(p * a.nblk + b) * a.post + col + i] = (uint8_t)bs[i].E;
-        }
-        if (WANT_CODES && a.transposed) {
-#pragma unroll
-            for (int i = 0; i < N; ++i)
-                a.scales[(p * a.post + col + i) * a.nblk + b] = (uint8_t)bs[i].E;
+            for (int i = 0; i < N; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)bs[i].E;
         }
         // transposed codes: 32 bytes per column, rows innermost
         uint32_t tc[N][kMaxRows / 4];
@@ -370,7 +381,10 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
                 c[i] = code_pair(q[4 * i], q[4 * i + 1], w[2 * i], a.fmt) |
                        (code_pair(q[4 * i + 2], q[4 * i + 3], w[2 * i + 1], a.fmt) << 16);
             reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
-            if ((threadIdx.x & (lanes_per_block - 1)) == 0) a.scales[v / lanes_per_block] = (uint8_t)fb.E;
+            if ((threadIdx.x & (lanes_per_block - 1)) == 0) {
+                const int64_t blk = v / lanes_per_block;
+                a.scales[scale_index(a, blk / a.nblk, blk % a.nblk, 0)] = (uint8_t)fb.E;
+            }
         }
     }
 }
@@ -408,10 +422,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles) {
     const bool ok = fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
     if (WANT_CODES) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (a.transposed) a.scales[(p * a.post + col + i) * a.nblk + b] = (uint8_t)fb[i].E;
-            else a.scales[(p * a.nblk + b) * a.post + col + i] = (uint8_t)fb[i].E;
-        }
+        for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
     }
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
     uint32_t tc[4][kMaxRows / 4];          // transposed codes: [column][4 rows per word]
@@ -512,10 +523,7 @@ __global__ void mx_generic_kernel(const MxArgs a, const int64_t ntiles) {
         m = max(m, __float_as_uint(load1<DT>(a.in, base + k * a.post)) & 0x7fffffffu);
     const BlockScale bs = block_scale(m, a);
     const bool dead = bs.inv == 0.0f;               // NaN block or flushed block
-    if (a.scales) {
-        if (a.transposed) a.scales[(p * a.post + j) * a.nblk + b] = (uint8_t)bs.E;
-        else a.scales[t] = (uint8_t)bs.E;
-    }
+    if (a.scales) a.scales[scale_index(a, p, b, j)] = (uint8_t)bs.E;
     const int64_t padded = a.nblk * a.block;
     for (int64_t k = k0; k < k0 + a.block; ++k) {
         if (k >= k1) {                              // padding of a ragged transposed block
