@@ -29,10 +29,36 @@
 
 namespace mxq {
 
+#ifdef MXQ_GEMM_TRACE
+#define TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 1000) { long long c_ = clock64(); reinterpret_cast<long long*>(g.status + 16)[slot] = c_; } } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
+
 constexpr int kBM = 128;          // tile rows (MMA M)
 constexpr int kBK = 128;          // K bytes per stage = four MMA K steps
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;       // two per tensor-memory lane quarter
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kSfChunk = 512;     // bytes of scales per 128 rows x 128 K
+
+// fp32 accumulator -> bfloat grid: integer rounding on the raw bits (formats
+// with eight exponent bits share fp32's exponent layout), branch-free.  The
+// constants are derived once per launch from (mode, bits dropped).
+struct OutRound {
+    uint32_t add;       // half step (half-away), half step minus one (half-even), 0 (toward zero / off)
+    uint32_t even_on;   // 1 for half-even
+    uint32_t keep;      // mask of the bits kept
+    uint32_t drop;
+};
+__device__ __forceinline__ uint32_t round_out_bits(uint32_t u, const OutRound& k) {
+    const uint32_t mag = u & 0x7fffffffu;
+    uint32_t r = (mag + k.add + ((mag >> k.drop) & k.even_on)) & k.keep;
+    r = mag >= kInf ? mag : r;                    // Inf / NaN pass through
+    return r | (u & 0x80000000u);
+}
+__device__ __forceinline__ float round_out_f(float v, const OutRound& k) {
+    return __uint_as_float(round_out_bits(__float_as_uint(v), k));
+}
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -45,8 +71,11 @@ struct GemmArgs {
     int64_t sfa_rows128, sfb_rows128;   // 128-row chunks per batch element
     uint32_t idesc;
     int out_dtype;              // DT_F32 or DT_BF16
-    int round_mode;             // RN_AWAY / RZ / RN_EVEN, or -1: no rounding
-    uint32_t drop;              // low bits removed by the bfloat rounding
+    OutRound rnd;               // bfloat rounding of the result
+    int epi_kind;               // 0/1/2: bf16 out, bfloat16 rounding nearest/floor/even, no bias; 3: generic
+    int bf16_exact;             // rounded values are bf16 values: pack upper halves
+    int c_tma;                  // output written by TMA stores (row pitch multiple of 16 bytes)
+    int dbg;
 };
 
 template <int BN, int STAGES>
@@ -56,29 +85,32 @@ struct GemmSmem {
     static constexpr int kSFA = kSfChunk;
     static constexpr int kSFB = (BN / 128) * kSfChunk;
     static constexpr int kStage = kA + kB + kSFA + kSFB;
-    static constexpr int kBarOff = STAGES * kStage;
+    static constexpr int kStgOff = STAGES * kStage;        // per epilogue warp: [32 rows x 64 bytes]
+    static constexpr int kBarOff = kStgOff + kEpiWarps * 2048;
     static constexpr int kTotal = kBarOff + 256 + 1024;   // barriers + alignment slack
 };
 
-// fp32 accumulator -> bfloat grid (integer rounding on the raw bits; formats
-// with eight exponent bits share fp32's exponent layout).
-__device__ __forceinline__ float round_out(float v, int mode, uint32_t drop) {
-    if (mode < 0) return v;
-    const uint32_t u = __float_as_uint(v);
-    const uint32_t mag = u & 0x7fffffffu;
-    if (mag >= kInf) return v;
-    const uint32_t mask = (1u << drop) - 1u;
-    uint32_t r = mag;
-    if (mode == RN_AWAY) r += 1u << (drop - 1);
-    else if (mode == RN_EVEN) r += (mask >> 1) + ((mag >> drop) & 1u);
-    r &= ~mask;
-    return __uint_as_float(r | (u & 0x80000000u));
+// Tile order: within a batch element, groups of kGroupM tile-rows are walked
+// column by column (m fastest inside a group), so the CTAs running at the same
+// time share a few A row-panels and a few B column-panels in L2 instead of
+// streaming the whole of B once per tile row.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int64_t t, const GemmArgs& g, int64_t tiles_per_batch,
+                                            int64_t& bi, int64_t& mt, int64_t& nt) {
+    bi = t / tiles_per_batch;
+    const int64_t r = t % tiles_per_batch;
+    const int64_t per_group = (int64_t)kGroupM * g.n_tiles;
+    const int64_t grp = r / per_group;
+    const int64_t i = r % per_group;
+    const int64_t rows = min((int64_t)kGroupM, g.m_tiles - grp * kGroupM);
+    mt = grp * kGroupM + i % rows;
+    nt = i / rows;
 }
 
 template <int BN, int STAGES, int ACC_BUFS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmArgs g) {
+               const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
     using S = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -101,7 +133,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
-        for (int b = 0; b < ACC_BUFS; ++b) { ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1); ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), 4); }
+        for (int b = 0; b < ACC_BUFS; ++b) { ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1); ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpiWarps); }
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -125,9 +157,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int64_t bi = t / tiles_per_batch;
-                const int64_t r = t % tiles_per_batch;
-                const int64_t mt = r / g.n_tiles, nt = r % g.n_tiles;   // n fastest: neighbours share the A tile
+                int64_t bi, mt, nt;
+                tile_coords(t, g, tiles_per_batch, bi, mt, nt);
                 for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -144,6 +175,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         ptx::bulk_load(ptx::smem_u32(st + S::kA + S::kB + S::kSFA + j * kSfChunk),
                                        g.sfb + ((bi * g.sfb_rows128 + nt * (BN / 128) + j) * g.k_blocks + kb) * kSfChunk,
                                        kSfChunk, bar);
+                    TRACE(0 + 2 * it);
                 }
             }
             if (!ok) {
@@ -169,6 +201,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!ptx::mbar_wait(ptx::smem_u32(&full[s]), ph, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after();
+                    TRACE(200 + 2 * it);
                     uint8_t* st = smem + (size_t)s * S::kStage;
                     const uint32_t a_addr = ptx::smem_u32(st);
                     const uint32_t b_addr = ptx::smem_u32(st + S::kA);
@@ -192,57 +225,105 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     ptx::tc_commit(ptx::smem_u32(&empty[s]));        // stage reusable once these MMAs retire
                 }
                 if (ok) ptx::tc_commit(ptx::smem_u32(&acc_full[buf]));
+                TRACE(400 + 2 * tile_i);
             }
         }
     } else {
         // ---------------- epilogue warps ----------------
+        // Warp (2 + e) drains lane quarter (warp & 3), column half (e >> 2) of the accumulator
+        // in chunks of 64 output bytes per row: tcgen05.ld -> rounding -> 64-byte-swizzled
+        // staging tile in shared memory -> TMA store (which also clips ragged M / N edges).
+        const int e = warp - 2;
         const int q = warp & 3;                               // the tensor-memory lane quarter this warp may read
+        const int half = e >> 2;
+        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * 2048);
+        const bool f32_out = g.out_dtype == DT_F32;
+        const int chunk_cols = f32_out ? 16 : 32;
+        const float* bp = reinterpret_cast<const float*>(g.bias);
         uint32_t tile_i = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
             const int buf = tile_i % ACC_BUFS;
             const uint32_t acc_ph = (tile_i / ACC_BUFS) & 1;
-            const int64_t bi = t / tiles_per_batch;
-            const int64_t r = t % tiles_per_batch;
-            const int64_t mt = r / g.n_tiles, nt = r % g.n_tiles;
+            int64_t bi, mt, nt;
+            tile_coords(t, g, tiles_per_batch, bi, mt, nt);
             if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buf]), acc_ph, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
-            const int64_t row = mt * kBM + q * 32 + lane;
+            if (warp == 2 && lane == 0) TRACE(600 + 2 * tile_i);
+            const int64_t row0 = mt * kBM + q * 32;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t v[16];
-                ptx::tmem_ld_32x32b_x16(taddr + c0, v);
-                ptx::tmem_ld_wait();
-                const int64_t col = nt * BN + c0;
-                if (row < g.M && col < g.N) {
-                    float f[16];
+            for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += chunk_cols) {
+                const int64_t col0 = nt * BN + c0;
+                if (col0 >= g.N) break;
+                uint32_t v[32];
+                uint32_t w[16];
+                const int tch = (c0 - half * (BN / 2)) / chunk_cols;
+                if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 0);
+                if (f32_out) {
+                    ptx::tmem_ld_32x32b_x16(taddr + c0, *reinterpret_cast<uint32_t(*)[16]>(v));
+                    ptx::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        f[i] = round_out(__uint_as_float(v[i]), g.round_mode, g.drop);
-                        if (g.bias) f[i] = round_out(f[i] + reinterpret_cast<const float*>(g.bias)[min(col + i, g.N - 1)], g.round_mode, g.drop);
+                        uint32_t b = round_out_bits(v[i], g.rnd);
+                        if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
+                        w[i] = b;
                     }
-                    const int64_t off = (bi * g.M + row) * g.N + col;
-                    if (col + 16 <= g.N && (g.N % 8) == 0) {
-                        if (g.out_dtype == DT_F32) {
-                            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.c) + off);
+                } else {
+                    ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+                    ptx::tmem_ld_wait();
+                    if (g.epi_kind == 0) {                     // half away: add half an ulp of bf16, keep the upper halves
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) o[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                        } else {
-                            uint32_t w[8];
+                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[2 * i] + 0x8000u, v[2 * i + 1] + 0x8000u, 0x7632);
+                    } else if (g.epi_kind == 1) {              // toward zero
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                                w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.c) + off);
-                            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[2 * i], v[2 * i + 1], 0x7632);
+                    } else if (g.epi_kind == 2) {              // half even: the hardware conversion
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                            w[i] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     } else {
-                        for (int i = 0; i < 16 && col + i < g.N; ++i) {
-                            if (g.out_dtype == DT_F32) reinterpret_cast<float*>(g.c)[off + i] = f[i];
-                            else reinterpret_cast<__nv_bfloat16*>(g.c)[off + i] = __float2bfloat16_rn(f[i]);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            uint32_t b0 = round_out_bits(v[2 * i], g.rnd);
+                            uint32_t b1 = round_out_bits(v[2 * i + 1], g.rnd);
+                            if (bp) {
+                                b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
+                                b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
+                            }
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b0), __uint_as_float(b1));
+                            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                }
+                if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 1);
+                if (g.c_tma) {
+                    if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
+                    __syncwarp();
+                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 2);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                    ptx::fence_proxy_async();
+                    __syncwarp();
+                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 3);
+                    if (lane == 0) {
+                        ptx::tma_store_3d(&tmap_c, stg, (int)col0, (int)row0, (int)bi);
+                        ptx::bulk_commit();
+                    }
+                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 4);
+                } else if (row0 + lane < g.M) {
+                    // row pitch not a multiple of 16 bytes: plain stores
+                    const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if (f32_out) {
+                            if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
+                        } else {
+                            if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
+                            if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
                         }
                     }
                 }
@@ -250,7 +331,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
+            if (warp == 2 && lane == 0) TRACE(800 + 2 * tile_i);
         }
+        if (lane == 0) ptx::bulk_wait_all();
     }
 
     // ---------------- teardown ----------------
@@ -302,21 +385,37 @@ static int* device_status_word() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!words[dev]) {
-        if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(words[dev], 0, sizeof(int));
+        if (cudaMalloc(&words[dev], 4096 * sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(words[dev], 0, 4096 * sizeof(int));
     }
     return words[dev];
 }
 
+// C [batch, M, N]: box = 64 bytes of a row x 32 rows, 64-byte swizzle
+static int make_output_map(CUtensorMap* m, void* base, int64_t batch, int64_t M, int64_t N, bool f32) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MXQ_ERR_CUDA;
+    const cuuint64_t es = f32 ? 4 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)N * es, (cuuint64_t)N * M * es};
+    cuuint32_t box[3] = {(cuuint32_t)(64 / es), 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
+}
+
 template <int BN, int STAGES, int ACC_BUFS>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g,
+                       cudaStream_t st) {
     using S = GemmSmem<BN, STAGES>;
     auto kern = gemm_mx_kernel<BN, STAGES, ACC_BUFS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
         return MXQ_ERR_CUDA;
     const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, g);
+    kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, tc, g);
     return check_launch();
 }
 
@@ -343,6 +442,7 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     if (!aligned16(a_codes) || !aligned16(b_codes) || !aligned16(a_scales) || !aligned16(b_scales) || !aligned16(c))
         return MXQ_ERR_ALIGN;
     if (batch > 0x7fffffff || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return MXQ_ERR_TOO_LARGE;
+    const int dbg = tile_n >> 16; tile_n &= 0xffff;
     int bn = (tile_n == 128 || tile_n == 256) ? tile_n : (N > 128 ? 256 : 128);
     // a 256-wide tile reads two 128-row scale chunks per K block; fall back to 128-wide
     // tiles when the scale buffer of B has an odd number of row chunks
@@ -357,15 +457,31 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     g.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, kBM, bn);
     g.out_dtype = out_dtype;
     const bool rounds = out_bfloat_bits >= 10 && out_bfloat_bits < 32 && out_round >= 0;
-    g.round_mode = rounds ? out_round : -1;
-    g.drop = rounds ? (uint32_t)(32 - out_bfloat_bits) : 0;
+    const uint32_t drop = rounds ? (uint32_t)(32 - out_bfloat_bits) : 0;
+    const uint32_t mask = rounds ? ((1u << drop) - 1u) : 0u;
+    g.rnd.drop = drop;
+    g.rnd.keep = ~mask;
+    g.rnd.even_on = (rounds && out_round == MXQ_ROUND_EVEN) ? 1u : 0u;
+    g.rnd.add = !rounds ? 0u : (out_round == MXQ_ROUND_NEAREST ? (1u << (drop - 1)) : (out_round == MXQ_ROUND_EVEN ? (mask >> 1) : 0u));
+    g.bf16_exact = rounds && drop >= 16;
+    g.epi_kind = (out_dtype == MXQ_BF16 && rounds && drop == 16 && !bias) ? out_round : 3;
     CUtensorMap ta, tb;
     int rc = make_operand_map(&ta, a_codes, batch, M, K, kBM);
     if (rc) return rc;
     rc = make_operand_map(&tb, b_codes, batch, N, K, bn);
     if (rc) return rc;
-    if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, g, (cudaStream_t)stream);
-    return launch_gemm<128, 6, 2>(ta, tb, g, (cudaStream_t)stream);
+    CUtensorMap tc;
+    const int64_t es = out_dtype == MXQ_F32 ? 4 : 2;
+    g.c_tma = (N * es) % 16 == 0;
+    g.dbg = dbg;
+    if (g.c_tma) {
+        rc = make_output_map(&tc, c, batch, M, N, out_dtype == MXQ_F32);
+        if (rc) return rc;
+    } else {
+        tc = ta;                                   // unused by the kernel
+    }
+    if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
+    return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
 }
 
 extern "C" int mxq_device_status(int clear) {
@@ -376,3 +492,11 @@ extern "C" int mxq_device_status(int clear) {
     if (clear && v != 0) cudaMemset(w, 0, sizeof(int));
     return v;
 }
+
+#ifdef MXQ_GEMM_TRACE
+extern "C" int mxq_debug_read(long long* out, int n) {
+    int* w = mxq::device_status_word();
+    if (!w) return -1;
+    return cudaMemcpy(out, w + 16, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+#endif
