@@ -1,0 +1,131 @@
+"""GPU parity of the block-scaled MX GEMM (tcgen05 kind::mxf8f6f4), through the
+C ABI, against the oracle's double-accumulated product of the dequantized
+operands.
+
+Tolerance (fp32 accumulation order only): before output rounding
+    |c - ref| <= 2^-22 * sum_k |a_k * b_k|
+(observed worst case on these inputs: 0.9 * 2^-24 of that sum); after bfloat16
+output rounding the result may differ from round(ref) by at most one bf16 ulp,
+and only where ref sits within the accumulation error of a rounding boundary."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+ROUNDS = {"nearest": 0, "floor": 1, "even": 2}
+
+
+@pytest.fixture(scope="module")
+def be():
+    from microxcaling_b200 import _backend
+    _backend.lib()
+    return _backend
+
+
+def quant_operand(be, X, fmt, rows_per_batch):
+    eb, mb, mn = oracle.FORMATS[fmt]
+    dq, codes, scales = be.quantize_mx(X, 8, eb, mb, mn, 32, X.dim() - 1, want_codes=True, gemm_layout=True,
+                                       rows_per_batch=rows_per_batch)
+    return dq, codes, scales, (1 if eb == 5 else 0)
+
+
+def run_case(be, batch, M, N, K, fa, fb, tile_n=0, out_dtype=torch.float32, bf_bits=0, rnd="nearest", bias=False,
+             seed=0):
+    g = torch.Generator().manual_seed(seed)
+    A = (torch.randn(batch * M, K, generator=g) * 2).to(torch.bfloat16).cuda()
+    B = (torch.randn(batch * N, K, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    dqa, ca, sa, ka = quant_operand(be, A, fa, M)
+    dqb, cb, sb, kb = quant_operand(be, B, fb, N)
+    bias_t = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16).float().cuda() if bias else None
+    C = be.gemm_mx(ca, sa, cb, sb, batch, M, N, K, ka, kb, out_dtype, bf_bits, ROUNDS[rnd], bias_t, tile_n)
+    torch.cuda.synchronize()
+    assert be.device_status() == 0
+    ref, refabs = oracle.gemm_nt(dqa.float().cpu().numpy().reshape(batch, M, K),
+                                 dqb.float().cpu().numpy().reshape(batch, N, K), want_abs=True)
+    return C.float().cpu().numpy().astype(np.float64), ref, refabs, (bias_t.cpu().numpy() if bias else None)
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128, 128), (1, 128, 128, 512), (1, 256, 384, 256), (3, 256, 128, 384),
+                                   (1, 200, 136, 256), (1, 200, 100, 256), (2, 384, 512, 256), (1, 2304, 512, 256),
+                                   (1, 1024, 1024, 4096)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_raw_accumulator(be, shape, tile_n):
+    batch, M, N, K = shape
+    got, ref, refabs, _ = run_case(be, batch, M, N, K, "fp8_e4m3", "fp8_e4m3", tile_n)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -22 * refabs + 1e-30)
+
+
+@pytest.mark.parametrize("fa,fb", [("fp8_e4m3", "fp8_e5m2"), ("fp8_e5m2", "fp8_e5m2"), ("fp8_e4m3", "fp4_e2m1"),
+                                   ("fp6_e3m2", "fp6_e3m2"), ("fp6_e2m3", "fp4_e2m1"), ("fp4_e2m1", "fp4_e2m1")])
+def test_gemm_format_pairs(be, fa, fb):
+    got, ref, refabs, _ = run_case(be, 2, 256, 256, 512, fa, fb)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -22 * refabs + 1e-30)
+
+
+def _bf_round(x, bits, mode):
+    import oracle as o
+    mn = 2.0 ** 127 * (2 ** (bits - 8) - 1) / 2 ** (bits - 9)
+    return o.quantize_elemwise(x.astype(np.float32), bits - 7, 8, mn, mode).astype(np.float64)
+
+
+@pytest.mark.parametrize("rnd", ["nearest", "floor", "even"])
+@pytest.mark.parametrize("out_dtype,bits", [(torch.bfloat16, 16), (torch.float32, 16), (torch.float32, 12),
+                                            (torch.bfloat16, 0)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_output_rounding(be, rnd, out_dtype, bits, bias):
+    got, ref, refabs, b = run_case(be, 1, 256, 384, 512, "fp8_e4m3", "fp8_e4m3", 0, out_dtype, bits, rnd, bias, seed=3)
+    tol = 2.0 ** -22 * refabs
+    eff_bits = bits if bits else (16 if out_dtype == torch.bfloat16 else 0)
+    mode = rnd if bits else "even"          # no bfloat rounding requested: only the bf16 storage cast (RNE)
+    if eff_bits:
+        bb = b[None, None, :] if b is not None else None
+
+        def model(x):
+            if bits == 0:                   # only the storage cast, applied once after the bias add
+                return _bf_round(x + bb if bb is not None else x, eff_bits, mode)
+            y = _bf_round(x, eff_bits, mode)
+            return _bf_round(y + bb, eff_bits, mode) if bb is not None else y
+        lo, hi, mid = model(ref - tol), model(ref + tol), model(ref)
+        assert np.all((got >= np.minimum(lo, hi)) & (got <= np.maximum(lo, hi)))
+        # and almost everywhere it is exactly the rounding of the reference value
+        assert np.mean(got == mid) > 0.995
+    else:
+        assert np.all(np.abs(got - ref - (b[None, None, :] if b is not None else 0)) <= tol + 1e-6)
+
+
+def test_gemm_nan_block_and_zero_rows(be):
+    A = torch.randn(128, 256).to(torch.bfloat16)
+    A[5, 40] = float("nan")
+    A[7] = 0
+    B = torch.randn(128, 256).to(torch.bfloat16)
+    dqa, ca, sa, _ = quant_operand(be, A.cuda(), "fp8_e4m3", 128)
+    dqb, cb, sb, _ = quant_operand(be, B.cuda(), "fp8_e4m3", 128)
+    C = be.gemm_mx(ca, sa, cb, sb, 1, 128, 128, 256, 0, 0, torch.float32, 0, 0, None, 0)[0].cpu().numpy()
+    assert np.isnan(C[5]).all() and not np.isnan(np.delete(C, 5, axis=0)).any()
+    assert (C[7] == 0).all()
+
+
+def test_gemm_rejects_bad_arguments(be):
+    z = torch.zeros(128 * 128, dtype=torch.uint8, device="cuda")
+    with pytest.raises(be.MxqError):
+        be.gemm_mx(z, z, z, z, 1, 128, 128, 96)           # K not a multiple of 128
+    with pytest.raises(be.MxqError):
+        be.gemm_mx(z, z, z, z, 1, 128, 128, 128, a_fmt=3)
+
+
+def test_gemm_transposed_operand_layout(be):
+    """The backward GEMMs contract over the row axis of their inputs: quantize
+    along axis -2 with transposed codes and multiply.  grad_w = g^T x."""
+    gen = torch.Generator().manual_seed(5)
+    Mtok, N, K = 512, 256, 384
+    G = torch.randn(Mtok, N, generator=gen).to(torch.bfloat16).cuda()
+    X = torch.randn(Mtok, K, generator=gen).to(torch.bfloat16).cuda()
+    eb, mb, mn = oracle.FORMATS["fp8_e5m2"]
+    dqg, cg, sg = be.quantize_mx(G, 8, eb, mb, mn, 32, 0, want_codes=True, transposed=True, gemm_layout=True)
+    dqx, cx, sx = be.quantize_mx(X, 8, eb, mb, mn, 32, 0, want_codes=True, transposed=True, gemm_layout=True)
+    assert cg.shape == (N, Mtok) and cx.shape == (K, Mtok)
+    C = be.gemm_mx(cg, sg, cx, sx, 1, N, K, Mtok, 1, 1, torch.float32, 0, 0, None, 0)[0].cpu().numpy().astype(np.float64)
+    ref, refabs = oracle.gemm_nt(dqg.float().cpu().numpy().T.copy(), dqx.float().cpu().numpy().T.copy(), want_abs=True)
+    assert np.all(np.abs(C - ref[0]) <= 2.0 ** -22 * refabs[0] + 1e-30)
