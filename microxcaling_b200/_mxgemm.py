@@ -1,0 +1,113 @@
+"""Shared GEMM plumbing of mx.linear / mx.matmul / mx.bmm.
+
+`mx_gemm` computes op1(in1) @ op2(in2) with each operand MX-quantized along
+its contraction axis and the result rounded to the vector format of mx_specs.
+On CUDA tensors with FP element formats and block size 32 it runs as
+quantize-to-packed-operand kernels plus the tcgen05 block-scaled GEMM; every
+other case (CPU tensors, fixed-point formats, odd block sizes, contraction
+length not a multiple of 128) follows the reference's construction: fake-quantize
+both operands, multiply with torch, round the result
+(mx/linear.py:62-96, mx/matmul.py:68-96, mx/bmm.py:40-62).
+"""
+import torch
+
+from .elemwise_ops import quantize_elemwise_op
+from .formats import ElemFormat, _get_format_params
+from .mx_ops import quantize_mx_op
+
+_MODE = {"nearest": 0, "floor": 1, "even": 2}
+_torch_matmul = torch.matmul
+
+
+def _fmt(f):
+    if f is None:
+        return None
+    return ElemFormat.from_str(f) if isinstance(f, str) else f
+
+
+def _fast_ok(in1, in2, f1, f2, specs, K, r1, r2, out_round):
+    if not (in1.is_cuda and in2.is_cuda) or f1 is None or f2 is None:
+        return False
+    if in1.dtype != in2.dtype or in1.dtype not in (torch.bfloat16, torch.float32, torch.float16):
+        return False
+    if specs["block_size"] != 32 or K % 128 != 0 or specs["shared_exp_method"] != "max":
+        return False
+    if specs["fp"] > 0 or (0 < specs["bfloat"] < 10):
+        return False
+    for f in (f1, f2):
+        ebits, mbits, _, _, _ = _get_format_params(f)
+        if ebits == 0 or mbits > 5:          # fixed point and wide formats have no fp8 container
+            return False
+    return r1 in _MODE and r2 in _MODE and out_round in _MODE
+
+
+def _pack(x, fmt, specs, rnd, contraction_last):
+    """x [..., R, K] (contraction_last) or [..., K, R] -> codes [batch, R, K], scales, container id."""
+    from . import _backend as be
+    ebits, mbits, _, max_norm, _ = _get_format_params(fmt)
+    scale_bits = specs["scale_bits"] or 8
+    x = x.contiguous()
+    if contraction_last:
+        R, K = x.shape[-2], x.shape[-1]
+        x2 = x.reshape(-1, K)
+        _, codes, scales = be.quantize_mx(x2, scale_bits, ebits, mbits, max_norm, 32, 1,
+                                          specs["mx_flush_fp32_subnorms"], _MODE[rnd], want_dq=False,
+                                          want_codes=True, gemm_layout=True, rows_per_batch=R)
+    else:
+        K, R = x.shape[-2], x.shape[-1]
+        x3 = x.reshape(-1, K, R)
+        _, codes, scales = be.quantize_mx(x3, scale_bits, ebits, mbits, max_norm, 32, 1,
+                                          specs["mx_flush_fp32_subnorms"], _MODE[rnd], want_dq=False,
+                                          want_codes=True, transposed=True, gemm_layout=True)
+    return codes, scales, (1 if ebits == 5 else 0)
+
+
+def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, trans1=False, trans2=False):
+    """op1(in1) @ op2(in2), op(x) = x^T of the last two dims when trans is set.
+
+    in1: [..., M, K] (or [..., K, M] with trans1); in2: [..., K, N] (or [..., N, K] with trans2),
+    in2 may have fewer leading dims than in1 (a shared 2-D matrix).  `bias` is an
+    already-quantized vector added after the first output rounding."""
+    fmt1, fmt2 = _fmt(fmt1), _fmt(fmt2)
+    M, K = (in1.shape[-1], in1.shape[-2]) if trans1 else (in1.shape[-2], in1.shape[-1])
+    N, K2 = (in2.shape[-2], in2.shape[-1]) if trans2 else (in2.shape[-1], in2.shape[-2])
+    assert K == K2, "contraction sizes differ"
+    lead1, lead2 = in1.shape[:-2], in2.shape[:-2]
+    shared_b = len(lead2) == 0 and len(lead1) > 0
+    fast = _fast_ok(in1, in2, fmt1, fmt2, specs, K, round1, round2, out_round) and in1.numel() > 0 and in2.numel() > 0
+    if fast and not shared_b and tuple(lead1) != tuple(lead2):
+        fast = False                          # general broadcasting: reference construction
+    if fast and shared_b and trans1:
+        fast = False
+    if fast:
+        from . import _backend as be
+        a_codes, a_scales, ka = _pack(in1, fmt1, specs, round1, not trans1)
+        b_codes, b_scales, kb = _pack(in2, fmt2, specs, round2, trans2)
+        if shared_b:
+            batch, rows = 1, in1.numel() // K       # leading dims of in1 fold into M
+            if rows != M:
+                # scales were laid out per [M]-row batch element; redo with all rows in one batch
+                a_codes, a_scales, ka = _pack(in1.reshape(-1, K), fmt1, specs, round1, True)
+        else:
+            batch, rows = (in1.numel() // (M * K)), M
+        bits = specs["bfloat"] if specs["bfloat"] >= 10 else 0
+        out = be.gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, rows, N, K, ka, kb,
+                         out_dtype=in1.dtype if in1.dtype != torch.float16 else torch.float32,
+                         bfloat_bits=bits, round_mode=_MODE[out_round],
+                         bias=None if bias is None else bias.reshape(-1))
+        if in1.dtype == torch.float16:
+            out = out.to(torch.float16)
+        return out.reshape(*lead1, M, N)
+
+    # reference construction
+    q1 = quantize_mx_op(in1, specs, elem_format=fmt1, axes=[-2 if trans1 else -1], round=round1)
+    q2 = quantize_mx_op(in2, specs, elem_format=fmt2, axes=[-1 if trans2 else -2], round=round2)
+    if q2.dtype != q1.dtype:
+        q2 = q2.to(q1.dtype)
+    a = q1.transpose(-1, -2) if trans1 else q1
+    b = q2.transpose(-1, -2) if trans2 else q2
+    out = _torch_matmul(a, b)
+    out = quantize_elemwise_op(out, mx_specs=specs, round=out_round)
+    if bias is not None:
+        out = quantize_elemwise_op(out + bias, mx_specs=specs, round=out_round)
+    return out

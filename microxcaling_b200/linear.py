@@ -1,0 +1,142 @@
+"""MX Linear: drop-in for the reference's mx/linear.py (LinearFunction :19-200,
+linear :203, Linear :221-291).
+
+Forward  y = Q(Q(MX(x) MX(w)^T) + b): operands MX-quantized along in_features.
+Backward grad_w = MX(g)^T MX(x) with both blocked along the token axis,
+         grad_x = MX(g) MX(w) with both blocked along out_features.
+Each product runs through `_mxgemm.mx_gemm` (packed operands + block-scaled
+tensor-core GEMM with the output rounding fused, where the formats allow it).
+"""
+import torch
+import torch.nn.functional as F
+
+from ._mxgemm import mx_gemm
+from .elemwise_ops import quantize_elemwise_op
+from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
+
+f_linear = F.linear
+torch_matmul = torch.matmul
+
+
+class LinearFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None):
+        bf_in = quantize_elemwise_op(input, mx_specs=mx_specs, round=mx_specs["round_output"])
+        if prequantized_weights:
+            assert weight.dtype == torch.bfloat16
+            bf_weight = weight
+        else:
+            bf_weight = quantize_elemwise_op(weight, mx_specs=mx_specs, round=mx_specs["round_weight"])
+        ctx.has_bias = bias is not None
+        bf_bias = None
+        if bias is not None:
+            if prequantized_weights:
+                assert bias.dtype == torch.bfloat16
+                bf_bias = bias
+            else:
+                bf_bias = quantize_elemwise_op(bias, mx_specs=mx_specs, round=mx_specs["round_weight"])
+        if mx_specs["quantize_backprop"]:
+            ctx.save_for_backward(bf_in, bf_weight)
+        else:
+            ctx.save_for_backward(input, weight)
+        if bf_weight.dtype != bf_in.dtype:
+            bf_weight = bf_weight.to(bf_in.dtype)
+        output = mx_gemm(bf_in, bf_weight, mx_specs["a_elem_format"], mx_specs["w_elem_format"], mx_specs,
+                         mx_specs["round_mx_output"], mx_specs["round_mx_output"], mx_specs["round_output"],
+                         bias=bf_bias, trans2=True)
+        ctx.mx_specs = get_backwards_mx_specs(mx_specs)
+        ctx.prequantized_weights = prequantized_weights
+        ctx.name = name
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        assert ctx.prequantized_weights is False, "Cannot use prequantized weights when training!"
+        input, weight = ctx.saved_tensors
+        sp = ctx.mx_specs
+        out_dim, in_dim = weight.shape
+        grad_output = quantize_elemwise_op(grad_output, mx_specs=sp, round=sp["round_grad_input"])
+
+        # grad_weight [out, in] = g^T x, blocks along the token axis.  A 3-D input
+        # blocks along its own sequence axis; that equals blocking the flattened
+        # token axis only when the sequence length is a multiple of the block.
+        if input.dim() > 2 and sp["block_size"] and input.shape[-2] % sp["block_size"] == 0:
+            g2, x2 = grad_output.reshape(-1, out_dim), input.reshape(-1, in_dim)
+        elif input.dim() <= 2:
+            g2, x2 = grad_output, input
+        else:
+            g2 = x2 = None
+        if g2 is not None:
+            grad_weight = mx_gemm(g2, x2, sp["a_elem_format_bp_ex"], sp["a_elem_format_bp"], sp,
+                                  sp["round_mx_grad_output_grad_weight"], sp["round_mx_input_grad_weight"],
+                                  sp["round_grad_weight"], trans1=True)
+        else:
+            from .mx_ops import quantize_mx_op
+            qg = quantize_mx_op(grad_output, sp, elem_format=sp["a_elem_format_bp_ex"], axes=[-2],
+                                round=sp["round_mx_grad_output_grad_weight"]).reshape(-1, out_dim)
+            qx = quantize_mx_op(input, sp, elem_format=sp["a_elem_format_bp"], axes=[-2],
+                                round=sp["round_mx_input_grad_weight"]).reshape(-1, in_dim)
+            grad_weight = quantize_elemwise_op(torch_matmul(qg.transpose(0, 1), qx), mx_specs=sp,
+                                               round=sp["round_grad_weight"])
+
+        # grad_input [..., in] = g w, blocks along out_features
+        grad_input = mx_gemm(grad_output, weight.to(grad_output.dtype), sp["a_elem_format_bp_os"],
+                             sp["w_elem_format_bp"], sp, sp["round_mx_grad_output_grad_input"],
+                             sp["round_mx_weight_grad_input"], sp["round_grad_input"])
+
+        grad_bias = None
+        if ctx.has_bias:
+            grad_bias = quantize_elemwise_op(grad_output.reshape(-1, out_dim).sum(0), mx_specs=sp,
+                                             round=sp["round_grad_weight"])
+        return (grad_input, grad_weight, grad_bias, None, None, None, None)
+
+
+def linear(input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None):
+    mx_assert_test(mx_specs)
+    if mx_specs is None:
+        return f_linear(input, weight, bias=bias)
+    mx_specs = apply_mx_specs(mx_specs)
+    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name)
+
+
+class Linear(torch.nn.Linear):
+    def __init__(self, in_features, out_features, bias=True, mx_specs=None, name=None):
+        mx_assert_test(mx_specs)
+        self.mx_none = mx_specs is None
+        self.name = name
+        self.prequantized_weights = False
+        self.mx_specs = apply_mx_specs(mx_specs)
+        super().__init__(in_features, out_features, bias)
+
+    def apply_mx_specs(self, mx_specs):
+        mx_assert_test(mx_specs)
+        self.mx_none = mx_specs is None
+        self.mx_specs = apply_mx_specs(mx_specs)
+
+    def append_name(self, postfix):
+        self.name += postfix
+
+    def prequantize_weights(self):
+        """Store weight and bias as bfloat16 once (inference only)."""
+        if self.mx_none:
+            return
+        assert self.mx_specs["round"] == "even", "Bfloat round should be 'even' for prequantizing weights."
+        assert torch.cuda.is_bf16_supported(), "Current device does not support bfloat16"
+        assert self.mx_specs["bfloat_subnorms"] is True, \
+            "Bfloat_subnorms should be set to True for prequantizing weights."
+        assert self.mx_specs["bfloat"] == 16, "Only Bfloat16 is supported for prequantizing weights."
+        with torch.no_grad():
+            self.weight.data = quantize_elemwise_op(self.weight.data, mx_specs=self.mx_specs,
+                                                    round=self.mx_specs["round_weight"]).to(torch.bfloat16)
+            if self.bias is not None:
+                self.bias.data = quantize_elemwise_op(self.bias.data, mx_specs=self.mx_specs,
+                                                      round=self.mx_specs["round_weight"]).to(torch.bfloat16)
+        self.prequantized_weights = True
+
+    def forward(self, inputs):
+        if self.mx_none:
+            return super().forward(inputs)
+        if self.prequantized_weights:
+            assert self.training is False, "Cannot use prequantized weights when training!"
+        return linear(input=inputs, weight=self.weight, bias=self.bias, mx_specs=self.mx_specs,
+                      prequantized_weights=self.prequantized_weights, name=self.name)

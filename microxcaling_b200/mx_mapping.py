@@ -1,0 +1,61 @@
+"""Process-wide injection of the MX operators into the torch namespaces
+(reference: mx/mx_mapping.py:26-122).  Every mapped function and module takes
+`mx_specs`; the injected wrappers supply it.  Only the operators this package
+implements are mapped: linear / matmul / mm / addmm / bmm, softmax, silu and
+the four arithmetic functions; the reference's convolution, normalisation,
+pooling, recurrent and remaining activation layers keep their stock torch
+implementations."""
+import torch
+
+from .activations import SiLU, silu
+from .bmm import bmm
+from .linear import Linear, linear
+from .matmul import MatMulFunction, matmul
+from .simd_ops import simd_add, simd_div, simd_mul, simd_sub
+from .softmax import Softmax, softmax
+from .specs import apply_mx_specs
+
+DEBUG = False
+torch_addmm = torch.addmm
+
+
+def tracer_decorator(func, mx_specs):
+    def wrapper(*args, **kwargs):
+        dtype = kwargs.pop("dtype", None)
+        if DEBUG:
+            print(func.__name__, mx_specs)
+        res = func(*args, mx_specs=mx_specs, **kwargs)
+        return res if dtype is None else res.to(dtype)
+    return wrapper
+
+
+def addmm_mx(bias, in1, in2, mx_specs=None, name=None):
+    if mx_specs is None:
+        return torch_addmm(bias, in1, in2)
+    return MatMulFunction.apply(in1, in2, bias, apply_mx_specs(mx_specs), name)
+
+
+MODULE_MAPPING = {"Linear": Linear, "SiLU": SiLU, "Softmax": Softmax}
+FUNCTION_MAPPING = {
+    "linear": linear, "matmul": matmul, "mm": matmul, "addmm": addmm_mx, "bmm": bmm,
+    "softmax": softmax, "silu": silu,
+    "add": simd_add, "sub": simd_sub, "mul": simd_mul, "div": simd_div,
+}
+
+
+def inject_pyt_ops(mx_specs):
+    """Replace torch.<fn>, torch.nn.functional.<fn> and torch.nn.<Module> with
+    the MX versions bound to `mx_specs`.  The MX operators captured the stock
+    torch callables at import time, so there is no recursion."""
+    def bind_module(cls):
+        def __init__(self, *args, **kwargs):
+            cls.__init__(self, *args, mx_specs=mx_specs, **kwargs)
+        return type(f"{cls.__name__}_inj", (cls,), {"__init__": __init__})
+
+    for k, v in FUNCTION_MAPPING.items():
+        if k in torch.__dict__:
+            torch.__dict__[k] = tracer_decorator(v, mx_specs)
+        if k in torch.nn.functional.__dict__:
+            torch.nn.functional.__dict__[k] = tracer_decorator(v, mx_specs)
+    for k, v in MODULE_MAPPING.items():
+        torch.nn.__dict__[k] = bind_module(v)

@@ -296,6 +296,33 @@ def main():
     run_mm("bmm_fp6", s_fp6, "bmm", (3,), 64, 128, 96)
     run_mm("matmul_fp8", s_fp8, "matmul", (), 96, 64, 128)
     run_mm("matmul_fp6_4d", s_fp6, "matmul", (2, 2), 32, 64, 32)
+    # bfloat-emulated vector layers between the GEMMs
+    s_vec = {"a_elem_format": "fp8_e4m3", "w_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16}
+    for tag, extra in (("vec_nearest", {}), ("vec_even_exp2", {"round": "even", "softmax_exp2": True,
+                                                               "vec_use_exp2": True})):
+        specs = dict(s_vec, **extra)
+        sp = finalize_mx_specs(dict(specs, custom_cuda=False))
+        x = bf(torch.randn(3, 24, 96, generator=g) * 2).requires_grad_()
+        go = bf(torch.randn(3, 24, 96, generator=g))
+        y = mx.softmax(x, dim=-1, mx_specs=sp); y.backward(go)
+        lay[tag + "_sm_x"], lay[tag + "_sm_go"], lay[tag + "_sm_y"], lay[tag + "_sm_gx"] = \
+            x.detach().numpy(), go.numpy(), y.detach().numpy(), x.grad.numpy()
+        x = bf(torch.randn(3, 24, 96, generator=g) * 2).requires_grad_()
+        y = mx.silu(x, mx_specs=sp); y.backward(go)
+        lay[tag + "_silu_x"], lay[tag + "_silu_y"], lay[tag + "_silu_gx"] = x.detach().numpy(), y.detach().numpy(), x.grad.numpy()
+        x = bf(torch.randn(3, 24, 96, generator=g) * 2).requires_grad_()
+        norm = mx.RMSNorm(96, eps=1e-5, mx_specs=sp)
+        with torch.no_grad():
+            norm.weight.copy_(bf(torch.rand(96, generator=g) + 0.5)); norm.bias.copy_(bf(torch.randn(96, generator=g) * 0.1))
+        y = norm(x); y.backward(go)
+        lay[tag + "_rms_x"], lay[tag + "_rms_w"], lay[tag + "_rms_b"] = x.detach().numpy(), norm.weight.detach().numpy(), norm.bias.detach().numpy()
+        lay[tag + "_rms_y"], lay[tag + "_rms_gx"], lay[tag + "_rms_gw"], lay[tag + "_rms_gb"] = \
+            y.detach().numpy(), x.grad.numpy(), norm.weight.grad.numpy(), norm.bias.grad.numpy()
+        a = bf(torch.randn(3, 24, 96, generator=g)).requires_grad_(); b = bf(torch.randn(24, 1, generator=g)).requires_grad_()
+        y = mx.simd_mul(a, b, mx_specs=sp); y.backward(go)
+        lay[tag + "_mul_a"], lay[tag + "_mul_b"], lay[tag + "_mul_y"], lay[tag + "_mul_ga"], lay[tag + "_mul_gb"] = \
+            a.detach().numpy(), b.detach().numpy(), y.detach().numpy(), a.grad.numpy(), b.grad.numpy()
+        lmeta.append({"op": "vec", "tag": tag, "specs": specs})
     np.savez_compressed(os.path.join(HERE, "layers.npz"),
                         meta=np.frombuffer(json.dumps(lmeta).encode(), np.uint8), **lay)
     print("layer cases:", len(lmeta))

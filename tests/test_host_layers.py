@@ -1,0 +1,149 @@
+"""CPU tests of the layer API (linear / matmul / bmm, softmax, RMSNorm, SiLU,
+simd ops, injection) against outputs recorded from the reference on the same
+seeded inputs.  On CPU tensors the layers follow the reference's construction
+with torch's own GEMM, so forward values and gradients must match exactly."""
+import numpy as np
+import pytest
+import torch
+
+import microxcaling_b200 as mx
+from microxcaling_b200.specs import finalize_mx_specs
+
+
+def _same(t, ref):
+    a = t.detach().numpy()
+    return np.array_equal(a, ref, equal_nan=True)
+
+
+def test_linear_matmul_bmm_match_reference(golden_layers):
+    meta, z = golden_layers
+    for m in meta:
+        if m["op"] == "vec":
+            continue
+        sp = finalize_mx_specs(dict(m["specs"], custom_cuda=False))
+        t = m["tag"]
+        go = torch.tensor(z[t + "_go"])
+        if m["op"] == "linear":
+            x = torch.tensor(z[t + "_x"], requires_grad=True)
+            w = torch.tensor(z[t + "_w"], requires_grad=True)
+            b = torch.tensor(z[t + "_b"], requires_grad=True) if m["bias"] else None
+            y = mx.linear(x, w, b, mx_specs=sp)
+            y.backward(go)
+            assert _same(y, z[t + "_y"]) and _same(x.grad, z[t + "_gx"]) and _same(w.grad, z[t + "_gw"]), t
+            if m["bias"]:
+                assert _same(b.grad, z[t + "_gb"]), t
+        else:
+            a = torch.tensor(z[t + "_a"], requires_grad=True)
+            b = torch.tensor(z[t + "_b"], requires_grad=True)
+            y = (mx.bmm if m["op"] == "bmm" else mx.matmul)(a, b, mx_specs=sp)
+            y.backward(go)
+            assert _same(y, z[t + "_y"]) and _same(a.grad, z[t + "_ga"]) and _same(b.grad, z[t + "_gb"]), t
+
+
+def test_vector_layers_match_reference(golden_layers):
+    meta, z = golden_layers
+    seen = 0
+    for m in meta:
+        if m["op"] != "vec":
+            continue
+        seen += 1
+        sp = finalize_mx_specs(dict(m["specs"], custom_cuda=False))
+        t = m["tag"]
+        go = torch.tensor(z[t + "_sm_go"])
+        x = torch.tensor(z[t + "_sm_x"], requires_grad=True)
+        y = mx.softmax(x, dim=-1, mx_specs=sp)
+        y.backward(go)
+        assert _same(y, z[t + "_sm_y"]) and _same(x.grad, z[t + "_sm_gx"]), t
+        x = torch.tensor(z[t + "_silu_x"], requires_grad=True)
+        y = mx.silu(x, mx_specs=sp)
+        y.backward(go)
+        assert _same(y, z[t + "_silu_y"]) and _same(x.grad, z[t + "_silu_gx"]), t
+        x = torch.tensor(z[t + "_rms_x"], requires_grad=True)
+        norm = mx.RMSNorm(96, eps=1e-5, mx_specs=sp)
+        with torch.no_grad():
+            norm.weight.copy_(torch.tensor(z[t + "_rms_w"]))
+            norm.bias.copy_(torch.tensor(z[t + "_rms_b"]))
+        y = norm(x)
+        y.backward(go)
+        assert _same(y, z[t + "_rms_y"]) and _same(x.grad, z[t + "_rms_gx"]), t
+        assert _same(norm.weight.grad, z[t + "_rms_gw"]) and _same(norm.bias.grad, z[t + "_rms_gb"]), t
+        a = torch.tensor(z[t + "_mul_a"], requires_grad=True)
+        b = torch.tensor(z[t + "_mul_b"], requires_grad=True)
+        y = mx.simd_mul(a, b, mx_specs=sp)
+        y.backward(go)
+        assert _same(y, z[t + "_mul_y"]) and _same(a.grad, z[t + "_mul_ga"]) and _same(b.grad, z[t + "_mul_gb"]), t
+    assert seen == 2
+
+
+def test_mx_specs_none_is_stock_torch():
+    # mx/tests/test_mxfp_none.py: with mx_specs=None every op is the torch op
+    torch.manual_seed(0)
+    x, w, b = torch.randn(5, 16), torch.randn(8, 16), torch.randn(8)
+    assert torch.equal(mx.linear(x, w, b, mx_specs=None), torch.nn.functional.linear(x, w, b))
+    assert torch.equal(mx.matmul(x, w.t(), mx_specs=None), torch.matmul(x, w.t()))
+    assert torch.equal(mx.bmm(x[None], w.t()[None], mx_specs=None), torch.bmm(x[None], w.t()[None]))
+    assert torch.equal(mx.softmax(x, -1, mx_specs=None), torch.softmax(x, -1))
+    assert torch.equal(mx.silu(x, mx_specs=None), torch.nn.functional.silu(x))
+    lin = mx.Linear(16, 8, mx_specs=None)
+    assert torch.equal(lin(x), torch.nn.functional.linear(x, lin.weight, lin.bias))
+    assert mx.quantize_bfloat(x, None) is x
+
+
+def test_quantization_disabled_matches_torch():
+    # mx/tests/test_linear.py:64-95: bfloat=0 and no element formats -> plain GEMM
+    torch.manual_seed(1)
+    sp = finalize_mx_specs({}, early_exit=False)
+    x = torch.randn(6, 32, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_()
+    lin = mx.Linear(32, 12, mx_specs=sp)
+    ref = torch.nn.Linear(32, 12)
+    ref.load_state_dict(lin.state_dict())
+    y, y2 = lin(x), ref(x2)
+    y.sum().backward()
+    y2.sum().backward()
+    assert torch.allclose(y, y2, atol=1e-6) and torch.allclose(x.grad, x2.grad, atol=1e-6)
+    assert torch.allclose(lin.weight.grad, ref.weight.grad, atol=1e-6)
+
+
+def test_inject_pyt_ops_and_restore():
+    from microxcaling_b200 import mx_mapping
+    saved = {k: torch.__dict__.get(k) for k in mx_mapping.FUNCTION_MAPPING}
+    saved_f = {k: torch.nn.functional.__dict__.get(k) for k in mx_mapping.FUNCTION_MAPPING}
+    saved_m = {k: torch.nn.__dict__.get(k) for k in mx_mapping.MODULE_MAPPING}
+    sp = finalize_mx_specs({"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16})
+    try:
+        mx_mapping.inject_pyt_ops(sp)
+        torch.manual_seed(2)
+        lin = torch.nn.Linear(64, 32, bias=False)
+        assert isinstance(lin, mx.Linear) and lin.mx_specs["w_elem_format"] == "fp4_e2m1"
+        x = torch.randn(4, 64)
+        y = lin(x)
+        y_direct = mx.linear(x, lin.weight, None, mx_specs=sp)
+        assert torch.equal(y, y_direct)
+        assert not torch.equal(y, saved_f["linear"](x, lin.weight))
+        z = torch.mul(torch.nn.functional.silu(y), y)
+        assert torch.equal(z, mx.simd_mul(mx.silu(y, mx_specs=sp), y, mx_specs=sp))
+        assert torch.matmul(x, lin.weight.t(), dtype=torch.float64).dtype == torch.float64
+    finally:
+        for k, v in saved.items():
+            if v is not None:
+                torch.__dict__[k] = v
+        for k, v in saved_f.items():
+            if v is not None:
+                torch.nn.functional.__dict__[k] = v
+        for k, v in saved_m.items():
+            torch.nn.__dict__[k] = v
+    assert torch.nn.Linear is saved_m["Linear"]
+
+
+def test_gradcheck_no_quantization():
+    # mx/tests/test_gradcheck.py:44-63: float64 gradcheck with default (no-quant) specs
+    sp = finalize_mx_specs({}, early_exit=False)
+    x = torch.randn(3, 8, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(5, 8, dtype=torch.float64, requires_grad=True)
+    b = torch.randn(5, dtype=torch.float64, requires_grad=True)
+    assert torch.autograd.gradcheck(lambda a, c, d: mx.linear(a, c, d, mx_specs=sp), (x, w, b))
+    a = torch.randn(2, 3, 4, dtype=torch.float64, requires_grad=True)
+    c = torch.randn(2, 4, 5, dtype=torch.float64, requires_grad=True)
+    assert torch.autograd.gradcheck(lambda u, v: mx.bmm(u, v, mx_specs=sp), (a, c))
+    assert torch.autograd.gradcheck(lambda u, v: mx.matmul(u, v, mx_specs=sp), (a, c))
