@@ -1,0 +1,133 @@
+"""GPU tests of the layer API: mx.linear / matmul / bmm forward and backward on
+CUDA tensors (packed operands + tcgen05 block-scaled GEMM with fused output
+rounding) against outputs recorded from the reference on the same seeded
+inputs (fp32 containers of bf16 values).
+
+Tolerance.  The GEMM accumulates in fp32 in a different order than the
+reference's library GEMM, and the result is then rounded to bfloat16, so an
+output can land on the neighbouring bf16 value when the exact sum sits within
+accumulation error of a rounding boundary: at most one bf16 ulp (2^-8 relative
+for the half-away mode... 2^-7 of the value), on a small fraction of elements;
+everything else must be equal."""
+import numpy as np
+import pytest
+import torch
+
+import microxcaling_b200 as mx
+from microxcaling_b200.specs import finalize_mx_specs
+
+pytestmark = pytest.mark.gpu
+
+
+def close_bf16(got, ref, name, min_exact=0.97):
+    a = got.detach().float().cpu().numpy().astype(np.float64)
+    b = ref.astype(np.float64)
+    assert a.shape == b.shape, name
+    ulp = np.maximum(np.abs(b), 1e-30) * 2.0 ** -7
+    ok = np.abs(a - b) <= ulp
+    assert ok.all(), (name, np.abs(a - b).max(), int((~ok).sum()))
+    exact = float((a == b).mean())
+    assert exact >= min_exact, (name, exact)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layers_match_reference(golden_layers, dtype):
+    meta, z = golden_layers
+    dev = "cuda"
+    for m in meta:
+        if m["op"] == "vec":
+            continue
+        sp = finalize_mx_specs(dict(m["specs"], custom_cuda=True))
+        t = m["tag"]
+        go = torch.tensor(z[t + "_go"]).to(dev, dtype)
+        if m["op"] == "linear":
+            x = torch.tensor(z[t + "_x"]).to(dev, dtype).requires_grad_()
+            w = torch.tensor(z[t + "_w"]).to(dev, dtype).requires_grad_()
+            b = torch.tensor(z[t + "_b"]).to(dev, dtype).requires_grad_() if m["bias"] else None
+            y = mx.linear(x, w, b, mx_specs=sp)
+            if sp["round"] != "even":      # bfloat16 + 'even' casts to torch.bfloat16, as the reference does
+                assert y.dtype == dtype, t
+            y.backward(go)
+            close_bf16(y, z[t + "_y"], t + ".y")
+            close_bf16(x.grad, z[t + "_gx"], t + ".gx")
+            close_bf16(w.grad, z[t + "_gw"], t + ".gw")
+            if m["bias"]:
+                close_bf16(b.grad, z[t + "_gb"], t + ".gb", min_exact=0.9)
+        else:
+            a = torch.tensor(z[t + "_a"]).to(dev, dtype).requires_grad_()
+            b = torch.tensor(z[t + "_b"]).to(dev, dtype).requires_grad_()
+            y = (mx.bmm if m["op"] == "bmm" else mx.matmul)(a, b, mx_specs=sp)
+            y.backward(go)
+            close_bf16(y, z[t + "_y"], t + ".y")
+            close_bf16(a.grad, z[t + "_ga"], t + ".ga")
+            close_bf16(b.grad, z[t + "_gb"], t + ".gb")
+
+
+def test_fast_path_is_taken(monkeypatch):
+    """FP8/FP6/FP4 formats with block 32 and K % 128 == 0 must reach the tensor-core GEMM."""
+    from microxcaling_b200 import _backend
+    calls = []
+    real = _backend.gemm_mx
+    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: calls.append(1) or real(*a, **k))
+    sp = finalize_mx_specs({"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32,
+                            "bfloat": 16, "custom_cuda": True})
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    lin = mx.Linear(512, 384, bias=True, mx_specs=sp).cuda().to(torch.bfloat16)
+    y = lin(x)
+    y.backward(torch.randn_like(y))
+    assert len(calls) == 3                      # forward, grad_weight, grad_input
+    assert _backend.device_status() == 0
+
+
+def test_vector_layers_on_gpu(golden_layers):
+    """softmax / SiLU / RMSNorm / simd_mul on CUDA: same chains of torch op + bfloat
+    rounding kernel; exp, reciprocal and sqrt differ between the CPU and CUDA
+    math libraries by an ulp of fp32, which after bfloat16 rounding shows up as
+    at most one bf16 ulp on a small fraction of elements."""
+    meta, z = golden_layers
+    for m in meta:
+        if m["op"] != "vec":
+            continue
+        sp = finalize_mx_specs(dict(m["specs"], custom_cuda=True))
+        t = m["tag"]
+        go = torch.tensor(z[t + "_sm_go"]).cuda()
+        x = torch.tensor(z[t + "_sm_x"]).cuda().requires_grad_()
+        y = mx.softmax(x, dim=-1, mx_specs=sp)
+        y.backward(go)
+        close_bf16(y, z[t + "_sm_y"], t + ".softmax", 0.9)
+        x = torch.tensor(z[t + "_silu_x"]).cuda().requires_grad_()
+        y = mx.silu(x, mx_specs=sp)
+        y.backward(go)
+        close_bf16(y, z[t + "_silu_y"], t + ".silu", 0.9)
+        x = torch.tensor(z[t + "_rms_x"]).cuda().requires_grad_()
+        norm = mx.RMSNorm(96, eps=1e-5, mx_specs=sp).cuda()
+        with torch.no_grad():
+            norm.weight.copy_(torch.tensor(z[t + "_rms_w"]))
+            norm.bias.copy_(torch.tensor(z[t + "_rms_b"]))
+        y = norm(x)
+        close_bf16(y, z[t + "_rms_y"], t + ".rmsnorm", 0.9)
+        a = torch.tensor(z[t + "_mul_a"]).cuda().requires_grad_()
+        b = torch.tensor(z[t + "_mul_b"]).cuda().requires_grad_()
+        y = mx.simd_mul(a, b, mx_specs=sp)
+        y.backward(go)
+        assert np.array_equal(y.detach().float().cpu().numpy(), z[t + "_mul_y"])
+        assert np.array_equal(a.grad.float().cpu().numpy(), z[t + "_mul_ga"])
+
+
+def test_attention_shaped_bmm_softmax_bmm():
+    """Config-4 shape at reduced head count: Q K^T -> softmax -> P V with fp6_e3m2 operands."""
+    torch.manual_seed(0)
+    H, S, D = 2, 256, 128
+    q, k, v = [(torch.randn(H, S, D) * 128 ** -0.25).to(torch.bfloat16) for _ in range(3)]
+    outs = {}
+    for dev in ("cpu", "cuda"):
+        sp = finalize_mx_specs({"a_elem_format": "fp6_e3m2", "block_size": 32, "bfloat": 16, "custom_cuda": dev == "cuda"})
+        Q, K, V = q.float().to(dev), k.float().to(dev), v.float().to(dev)
+        s = mx.bmm(Q, K.transpose(-1, -2).contiguous(), mx_specs=sp)
+        outs[dev] = (s, V, sp)
+    close_bf16(outs["cuda"][0], outs["cpu"][0].numpy(), "scores")
+    # second product on identical probabilities, so only the GEMM differs
+    p = mx.softmax(outs["cpu"][0], dim=-1, mx_specs=outs["cpu"][2])
+    o_cpu = mx.bmm(p, outs["cpu"][1], mx_specs=outs["cpu"][2])
+    o_gpu = mx.bmm(p.cuda(), outs["cuda"][1], mx_specs=outs["cuda"][2])
+    close_bf16(o_gpu, o_cpu.numpy(), "out")
