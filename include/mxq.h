@@ -142,6 +142,29 @@ int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, 
 /* Bytes of a scales buffer in the GEMM layout for a [batch, rows, K] operand. */
 int64_t mxq_sf_bytes(int64_t batch, int64_t rows, int64_t K);
 
+/*
+ * Forward of an MX linear layer whose weights were packed once:
+ *   y[M,N] = round(MX(x)[M,K] * W[N,K]^T (+ bias)),
+ * i.e. the activation quantization (mx/linear.py:62-68, block 32 along K) and
+ * the product with its output rounding (mx/linear.py:83-96) in one call.
+ *   x          [M, K], x_dtype
+ *   a_*        element format, rounding, scale width and subnormal flush of
+ *              the activation quantization (as in mxq_quantize_mx)
+ *   w_codes, w_scales, w_fmt   the weight as mxq_quantize_mx packed it
+ *              ([N, K] codes, scales in MXQ_SCALES_GEMM_LAYOUT, container id)
+ *   y, y_dtype, out_bfloat_bits, out_round, bias   as in mxq_gemm_mx
+ *   workspace  device memory for the packed activations, 256-byte aligned,
+ *              at least mxq_linear_workspace_bytes(M, K) bytes; its first
+ *              4 bytes are the status word of this call (0, or MXQ_ERR_DEVICE)
+ * K must be a multiple of 128.  Allocates nothing.
+ */
+int mxq_linear_fwd(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits, int a_mbits,
+                   float a_max_norm, int a_round, int scale_bits, int flush_fp32_subnorms,
+                   const void* w_codes, const void* w_scales, int64_t N, int w_fmt, void* y, int y_dtype,
+                   int out_bfloat_bits, int out_round, const void* bias, void* workspace,
+                   int64_t workspace_bytes, void* stream);
+int64_t mxq_linear_workspace_bytes(int64_t M, int64_t K);
+
 /* Synchronously reads (and optionally clears) the current device's status word:
  * 0, or MXQ_ERR_DEVICE after a kernel timed out on a wait. */
 int mxq_device_status(int clear);

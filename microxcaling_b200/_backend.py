@@ -44,6 +44,10 @@ def lib():
         L.mxq_sf_bytes.argtypes = [i64, i64, i64]
         L.mxq_sf_bytes.restype = i64
         L.mxq_device_status.argtypes = [i32]
+        L.mxq_linear_fwd.argtypes = [vp, i32, i64, i64, i32, i32, f32, i32, i32, i32, vp, vp, i64, i32, vp, i32,
+                                     i32, i32, vp, vp, i64, vp]
+        L.mxq_linear_workspace_bytes.argtypes = [i64, i64]
+        L.mxq_linear_workspace_bytes.restype = i64
         L.mxq_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, vp]
         L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
@@ -161,6 +165,26 @@ def gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, M, N, K, a_fmt=0, b_fmt
                                 batch, M, N, K, a_fmt, b_fmt, _DT[out.dtype], int(bfloat_bits), int(round_mode),
                                 _ptr(bias), int(tile_n), _stream(a_codes)))
     return out
+
+
+def linear_fwd(x, w_codes, w_scales, w_fmt, a_ebits, a_mbits, a_max_norm, a_round=0, scale_bits=8, flush=False,
+               out_dtype=None, bfloat_bits=16, out_round=0, bias=None, workspace=None):
+    """y = round(MX(x) @ W^T (+ bias)) with pre-packed W; see mxq_linear_fwd.  Returns (y, workspace)."""
+    _require_cuda(x, "x")
+    M, K = x.shape
+    N = w_codes.shape[0]
+    need = lib().mxq_linear_workspace_bytes(M, K)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    y = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        check(lib().mxq_linear_fwd(_ptr(x), _DT[x.dtype], M, K, int(a_ebits), int(a_mbits), float(a_max_norm),
+                                   int(a_round), int(scale_bits), int(bool(flush)), _ptr(w_codes), _ptr(w_scales),
+                                   N, int(w_fmt), _ptr(y), _DT[y.dtype], int(bfloat_bits), int(out_round),
+                                   _ptr(bias), _ptr(workspace), workspace.numel(), _stream(x)))
+    return y, workspace
 
 
 def device_status(clear=True):

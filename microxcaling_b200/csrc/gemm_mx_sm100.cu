@@ -75,7 +75,6 @@ struct GemmArgs {
     int epi_kind;               // 0/1/2: bf16 out, bfloat16 rounding nearest/floor/even, no bias; 3: generic
     int bf16_exact;             // rounded values are bf16 values: pack upper halves
     int c_tma;                  // output written by TMA stores (row pitch multiple of 16 bytes)
-    int dbg;
 };
 
 template <int BN, int STAGES>
@@ -426,11 +425,13 @@ extern "C" int64_t mxq_sf_bytes(int64_t batch, int64_t rows, int64_t K) {
     return batch * ((rows + 127) / 128) * ((K + 127) / 128) * 512;
 }
 
-extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
-                           void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
-                           int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
-                           void* stream) {
-    using namespace mxq;
+namespace mxq {
+// The GEMM with the device status word supplied by the caller (4 bytes of
+// device memory the kernel writes MXQ_ERR_DEVICE to when it gives up on a wait).
+int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                        void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
+                        int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
+                        int* status_word, void* stream) {
     if (batch < 0 || M < 0 || N < 0 || K < 0) return MXQ_ERR_BAD_ARG;
     if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
     if (!a_codes || !a_scales || !b_codes || !b_scales || !c) return MXQ_ERR_BAD_ARG;
@@ -442,14 +443,13 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     if (!aligned16(a_codes) || !aligned16(b_codes) || !aligned16(a_scales) || !aligned16(b_scales) || !aligned16(c))
         return MXQ_ERR_ALIGN;
     if (batch > 0x7fffffff || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return MXQ_ERR_TOO_LARGE;
-    const int dbg = tile_n >> 16; tile_n &= 0xffff;
     int bn = (tile_n == 128 || tile_n == 256) ? tile_n : (N > 128 ? 256 : 128);
     // a 256-wide tile reads two 128-row scale chunks per K block; fall back to 128-wide
     // tiles when the scale buffer of B has an odd number of row chunks
     if (bn == 256 && ((N + 127) / 128) % 2 != 0) bn = 128;
     GemmArgs g;
     g.sfa = (const uint8_t*)a_scales; g.sfb = (const uint8_t*)b_scales; g.c = c; g.bias = bias;
-    g.status = device_status_word();
+    g.status = status_word;
     if (!g.status) return MXQ_ERR_CUDA;
     g.M = M; g.N = N; g.K = K; g.batch = batch;
     g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = K / kBK;
@@ -473,7 +473,6 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     CUtensorMap tc;
     const int64_t es = out_dtype == MXQ_F32 ? 4 : 2;
     g.c_tma = (N * es) % 16 == 0;
-    g.dbg = dbg;
     if (g.c_tma) {
         rc = make_output_map(&tc, c, batch, M, N, out_dtype == MXQ_F32);
         if (rc) return rc;
@@ -482,6 +481,19 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     }
     if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
     return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
+}
+}  // namespace mxq
+
+extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                           void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
+                           int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
+                           void* stream) {
+    if (batch < 0 || M < 0 || N < 0 || K < 0) return MXQ_ERR_BAD_ARG;
+    if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
+    int* word = mxq::device_status_word();
+    if (!word) return MXQ_ERR_CUDA;
+    return mxq::gemm_mx_with_status(a_codes, a_scales, b_codes, b_scales, c, batch, M, N, K, a_fmt, b_fmt, out_dtype,
+                                    out_bfloat_bits, out_round, bias, tile_n, word, stream);
 }
 
 extern "C" int mxq_device_status(int clear) {

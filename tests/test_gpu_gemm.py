@@ -129,3 +129,21 @@ def test_gemm_transposed_operand_layout(be):
     C = be.gemm_mx(cg, sg, cx, sx, 1, N, K, Mtok, 1, 1, torch.float32, 0, 0, None, 0)[0].cpu().numpy().astype(np.float64)
     ref, refabs = oracle.gemm_nt(dqg.float().cpu().numpy().T.copy(), dqx.float().cpu().numpy().T.copy(), want_abs=True)
     assert np.all(np.abs(C - ref[0]) <= 2.0 ** -22 * refabs[0] + 1e-30)
+
+
+def test_linear_fwd_composite_equals_two_calls(be):
+    """mxq_linear_fwd (quantize into a workspace + GEMM) == mxq_quantize_mx followed by mxq_gemm_mx."""
+    gen = torch.Generator().manual_seed(9)
+    for (M, K, N) in ((256, 512, 384), (200, 256, 136)):
+        x = torch.randn(M, K, generator=gen).to(torch.bfloat16).cuda()
+        w = (torch.randn(N, K, generator=gen) * 0.1).to(torch.bfloat16).cuda()
+        bias = torch.randn(N, generator=gen).to(torch.bfloat16).float().cuda()
+        ea, ma, na = oracle.FORMATS["fp8_e4m3"]
+        ew, mw, nw = oracle.FORMATS["fp4_e2m1"]
+        _, wc, ws = be.quantize_mx(w, 8, ew, mw, nw, 32, 1, want_dq=False, want_codes=True, gemm_layout=True)
+        _, xc, xs = be.quantize_mx(x, 8, ea, ma, na, 32, 1, want_dq=False, want_codes=True, gemm_layout=True)
+        want = be.gemm_mx(xc, xs, wc, ws, 1, M, N, K, 0, 0, torch.bfloat16, 16, 0, bias)[0]
+        got, wsp = be.linear_fwd(x, wc, ws, 0, ea, ma, na, bias=bias)
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        assert int(wsp[:4].view(torch.int32).item()) == 0
