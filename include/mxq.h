@@ -165,6 +165,32 @@ int mxq_linear_fwd(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits
                    int64_t workspace_bytes, void* stream);
 int64_t mxq_linear_workspace_bytes(int64_t M, int64_t K);
 
+/*
+ * mxq_linear_fwd for callers that cannot allocate and have no buffer to lend.
+ * No counterpart in the reference (which allocates a fresh tensor in every
+ * call, mx/cpp/mx.cu:27-28).  Same arguments and result as mxq_linear_fwd
+ * without the workspace: the packed activations and the status word live in a
+ * fixed array inside the library image, 256 B + 33 MiB of device memory that
+ * every GPU loading libmxq.so holds until the process exits.
+ *   - Limit: ceil(M/128)*128 * K <= mxq_linear_static_max_elems() (32 Mi, e.g.
+ *     8192 x 4096); larger shapes return MXQ_ERR_TOO_LARGE and launch nothing.
+ *   - Calls cudaMalloc / cudaFree never; the first call on each device looks up
+ *     the array's device address (cudaGetSymbolAddress) and should be made
+ *     before any stream capture begins.
+ *   - All calls on a device share the array: two calls whose kernels can
+ *     overlap on the GPU (different streams) race on it; calls on one stream
+ *     are ordered and safe.  The array keeps the last call's contents; each
+ *     call re-zeroes the parts it relies on (status word, scale region).
+ *   - mxq_linear_static_status() reads the status word of the last call
+ *     (synchronous): 0, or MXQ_ERR_DEVICE if a kernel gave up on a wait.
+ */
+int mxq_linear_fwd_static(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits, int a_mbits,
+                          float a_max_norm, int a_round, int scale_bits, int flush_fp32_subnorms,
+                          const void* w_codes, const void* w_scales, int64_t N, int w_fmt, void* y,
+                          int y_dtype, int out_bfloat_bits, int out_round, const void* bias, void* stream);
+int64_t mxq_linear_static_max_elems(void);
+int mxq_linear_static_status(void);
+
 /* Synchronously reads (and optionally clears) the current device's status word:
  * 0, or MXQ_ERR_DEVICE after a kernel timed out on a wait. */
 int mxq_device_status(int clear);

@@ -81,3 +81,69 @@ extern "C" int mxq_linear_fwd(const void* x, int x_dtype, int64_t M, int64_t K, 
     return linear_fwd_impl(x, x_dtype, M, K, a_ebits, a_mbits, a_max_norm, a_round, scale_bits, flush_fp32_subnorms,
                            w_codes, w_scales, N, w_fmt, y, y_dtype, out_bfloat_bits, out_round, bias, workspace, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Variant for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the time they need a
+// linear layer: a serving process that reserved all device memory for its own
+// pools at start-up has nothing left to hand out, and a caller inside a
+// latency-bound loop cannot afford the device-wide synchronisation an
+// allocation implies.  Such callers also often have no spare buffer to pass as
+// the workspace of mxq_linear_fwd.  mxq_linear_fwd_static therefore keeps the
+// packed activations and the status word in a fixed array that is part of the
+// library image: every GPU that loads libmxq.so holds kLinearStaticBytes of
+// device memory for it until the process exits.
+//
+// In host code `g_linear_scratch` is only a handle for the device symbol, not
+// an address a kernel could use; the device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and passed on.
+// ---------------------------------------------------------------------------
+namespace mxq {
+constexpr int64_t kLinearStaticMaxElems = int64_t(32) << 20;          // ceil(M/128)*128 * K
+constexpr int64_t kLinearStaticBytes = 256 + kLinearStaticMaxElems + kLinearStaticMaxElems / 32;
+static __device__ __align__(256) unsigned char g_linear_scratch[kLinearStaticBytes];
+
+static void* linear_static_base(int* rc_out) {
+    static void* base[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *rc_out = MXQ_ERR_CUDA; return nullptr; }
+    if (!base[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_linear_scratch) != cudaSuccess || !p) { *rc_out = MXQ_ERR_CUDA; return nullptr; }
+        base[dev] = p;
+    }
+    *rc_out = MXQ_OK;
+    return base[dev];
+}
+}  // namespace mxq
+
+extern "C" int64_t mxq_linear_static_max_elems(void) { return mxq::kLinearStaticMaxElems; }
+
+extern "C" int mxq_linear_fwd_static(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits, int a_mbits,
+                                     float a_max_norm, int a_round, int scale_bits, int flush_fp32_subnorms,
+                                     const void* w_codes, const void* w_scales, int64_t N, int w_fmt, void* y,
+                                     int y_dtype, int out_bfloat_bits, int out_round, const void* bias,
+                                     void* stream) {
+    using namespace mxq;
+    int rc = check_linear_args(x, M, K, w_codes, w_scales, N, y, a_ebits, a_mbits);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return MXQ_OK;
+    const int64_t m_pad = (M + 127) / 128 * 128;
+    if (m_pad > kLinearStaticMaxElems / K) return MXQ_ERR_TOO_LARGE;   // ceil(M/128)*128*K beyond the fixed array
+    void* base = linear_static_base(&rc);
+    if (!base) return rc;
+    // The array still holds the previous call's packed activations; linear_fwd_impl zeroes the
+    // status word and the scale region (its padding rows are read but never written) before use.
+    return linear_fwd_impl(x, x_dtype, M, K, a_ebits, a_mbits, a_max_norm, a_round, scale_bits, flush_fp32_subnorms,
+                           w_codes, w_scales, N, w_fmt, y, y_dtype, out_bfloat_bits, out_round, bias, base, stream);
+}
+
+extern "C" int mxq_linear_static_status(void) {
+    int rc = 0;
+    void* base = mxq::linear_static_base(&rc);
+    if (!base) return rc;
+    int v = 0;
+    if (cudaMemcpy(&v, base, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MXQ_ERR_CUDA;
+    return v;
+}
