@@ -39,6 +39,8 @@ extern "C" int mxq_quantize_mx(const void* in, void* out, void* codes, void* sca
     a.sf_gemm = (flags & MXQ_SCALES_GEMM_LAYOUT) != 0;
     a.sf_rpb = sf_rows_per_batch > 0 ? sf_rows_per_batch : (a.transposed ? post : pre);
     if (a.sf_gemm && (block != 32 || (!a.transposed && post != 1))) return MXQ_ERR_UNSUPPORTED;
+    a.div_nblk.set((uint32_t)std::min<int64_t>(a.nblk, 0xffffffffLL));
+    a.div_rpb.set((uint32_t)std::min<int64_t>(a.sf_rpb, 0xffffffffLL));
     a.fmt = make_fmt(elem_ebits, elem_mbits, elem_max_norm, rmode);
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {

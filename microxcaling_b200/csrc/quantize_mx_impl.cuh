@@ -23,6 +23,24 @@
 
 namespace mxq {
 
+// Division of a 32-bit number by a launch-invariant divisor: one multiply-high
+// and two shifts instead of the long software division sequence.
+struct FastDiv {
+    uint32_t d, m, s1, s2;
+    __host__ void set(uint32_t div) {
+        d = div ? div : 1;
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        m = (uint32_t)((((1ull << l) - d) << 32) / d + 1);
+        s1 = l < 1 ? l : 1;
+        s2 = l > 0 ? l - 1 : 0;
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const {
+        const uint32_t t = __umulhi(m, n);
+        return (t + ((n - t) >> s1)) >> s2;
+    }
+};
+
 struct MxArgs {
     const void* in;
     void* out;
@@ -38,8 +56,22 @@ struct MxArgs {
     int transposed;
     int sf_gemm;            // scales in the 512-byte chunk layout of the GEMM
     int64_t sf_rpb;         // rows per batch element for that layout
+    FastDiv div_nblk;       // last-axis kernels: block index -> (row, block in row)
+    FastDiv div_rpb;        // row -> (batch, row in batch)
     ElemFmt fmt;
 };
+
+// Last-axis kernels: byte index of the scale of linear block index `blk`
+// (row-major over [rows, nblk]); 32-bit arithmetic with invariant divisors.
+__device__ __forceinline__ int64_t scale_index_last(const MxArgs& a, uint32_t blk) {
+    if (!a.sf_gemm) return blk;
+    const uint32_t row_all = a.div_nblk.div(blk);
+    const uint32_t b = blk - row_all * (uint32_t)a.nblk;
+    const uint32_t batch = a.div_rpb.div(row_all);
+    const uint32_t row = row_all - batch * (uint32_t)a.sf_rpb;
+    const int64_t r128 = (a.sf_rpb + 127) >> 7, kb4 = (a.nblk + 3) >> 2;
+    return ((batch * r128 + (row >> 7)) * kb4 + (b >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (b & 3);
+}
 
 // Byte index of the scale of block b of (pre index p, post index j).
 __device__ __forceinline__ int64_t scale_index(const MxArgs& a, int64_t p, int64_t b, int64_t j) {
@@ -80,26 +112,30 @@ __device__ __forceinline__ float quant_abs(uint32_t xb, const BlockScale& s, con
 }
 
 // Per-block constants of the unscaled fast path (see round_unscaled_abs).
+// The fast path needs the rounding constants to be normal, finite floats, which
+// holds when the block maximum lies in a wide middle range of exponents; other
+// blocks (tiny or huge maxima, NaN/Inf, flushed) are marked !ok and go through a
+// compact scaled-domain loop instead.
 struct FastBlock {
     float cmin;      // 2^(emin + s) * scale
     float maxn;      // max_norm * scale
-    bool ok;         // the block's exponents allow the fast path
+    float inv;       // 1 / scale, for the element codes
     int E;           // biased scale exponent (E8M0 byte)
+    bool ok;
 };
 
 __device__ __forceinline__ FastBlock fast_block(uint32_t amax_bits, const MxArgs& a) {
     FastBlock f;
     const int Eraw = (int)(amax_bits >> 23);
     const int E = scale_exp_from_absmax(amax_bits, a.fmt.emax_elem, a.scale_emax);
-    const int emin_biased = (int)(a.fmt.emin_field >> 23);           // emin + 127
     const bool zero = amax_bits == 0;
-    // cmin's exponent field (emin + E + s) and x * 2^s must stay normal and
-    // finite; NaN and flushed blocks take the scaled-domain routine.
-    f.ok = zero || (E != 255 && E + emin_biased - 127 >= 1 && Eraw <= 228 && Eraw >= 1);
     const int Ec = zero ? 127 : E;
+    const int field = (int)(a.fmt.emin_field >> 23) + (int)(a.fmt.k_field >> 23) + Ec - 127;
+    f.ok = zero || (Eraw >= 48 && Eraw <= 200 && E != 255 && field >= 1 && field < 254);
+    f.E = E;
     f.cmin = __uint_as_float(a.fmt.emin_field + a.fmt.k_field + ((uint32_t)(Ec - 127) << 23));
     f.maxn = __uint_as_float(__float_as_uint(a.fmt.max_norm) + ((uint32_t)(Ec - 127) << 23));
-    f.E = E;
+    f.inv = inv_pow2_from_field(Ec);
     return f;
 }
 
@@ -162,10 +198,8 @@ mx_lastaxis_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block
                 for (int i = 0; i < N / 4; ++i) c[i] = pack_codes4(&q[4 * i], &xb[u][4 * i], a.fmt);
                 if (N == 4) *reinterpret_cast<uint32_t*>(a.codes + v * N) = c[0];
                 else *reinterpret_cast<uint2*>(a.codes + v * N) = make_uint2(c[0], c[N / 4 - 1]);
-                if ((threadIdx.x & (lanes_per_block - 1)) == 0) {
-                    const int64_t blk = v / lanes_per_block;
-                    a.scales[scale_index(a, blk / a.nblk, blk % a.nblk, 0)] = (uint8_t)bs.E;
-                }
+                if ((threadIdx.x & (lanes_per_block - 1)) == 0)
+                    a.scales[scale_index_last(a, (uint32_t)(v / lanes_per_block))] = (uint8_t)bs.E;
             }
             if (WANT_DQ) {
                 uint32_t ob[N];
@@ -310,29 +344,47 @@ __device__ __forceinline__ uint32_t quant_pair_bf16(uint32_t w, float cmin_lo, f
     return p | (w & 0x80008000u);
 }
 
-// scaled-domain fallback for one bf16 element held as fp32 bits
-template <int MODE>
-__device__ __forceinline__ uint32_t quant_slow_bits(uint32_t xb, const BlockScale& bs, const ElemFmt& f, float& q) {
-    q = quant_abs<MODE>(xb, bs, f);
-    return __float_as_uint(q * bs.scale) | (xb & 0x80000000u);
-}
+// Code container of the packed operand, fixed at compile time in the bf16
+// kernels so that only one conversion is emitted.
+enum : int { CK_NONE = 0, CK_E4M3 = 1, CK_E5M2 = 2 };
 
-__device__ __forceinline__ uint32_t code_pair(float q_lo, float q_hi, uint32_t w, const ElemFmt& f) {
-    // signed scaled values -> two code bytes (lo element in bits 0..7)
+// two scaled magnitudes + the signs of the source pair w -> two code bytes (lo element in bits 0..7)
+template <int CK>
+__device__ __forceinline__ uint32_t code_pair(float q_lo, float q_hi, uint32_t w) {
     const float sl = __uint_as_float(__float_as_uint(q_lo) | ((w << 16) & 0x80000000u));
     const float sh = __uint_as_float(__float_as_uint(q_hi) | (w & 0x80000000u));
-    if (f.ebits == 0)
-        return (uint32_t)(__float2int_rn(ldexpf(sl, f.mbits - 2)) & 0xff) |
-               ((uint32_t)(__float2int_rn(ldexpf(sh, f.mbits - 2)) & 0xff) << 8);
-    return f.ebits == 5 ? encode2_e5m2(sl, sh) : encode2_e4m3(sl, sh);
+    return CK == CK_E5M2 ? encode2_e5m2(sl, sh) : encode2_e4m3(sl, sh);
+}
+
+// Compact path for the blocks the fast path excludes: `rows` elements with
+// stride `stride` (in elements), re-read from global memory, scaled-domain
+// arithmetic, rolled loop (it runs rarely and must stay small).
+template <int MODE, int CK>
+__device__ __forceinline__ void bf16_block_slow(const MxArgs& a, const uint16_t* in, int64_t first, int64_t stride,
+                                                int rows, uint32_t amax, uint8_t* codes_dst, int64_t codes_stride,
+                                                int pad_to) {
+    const BlockScale bs = block_scale(amax, a);
+    uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+#pragma unroll 1
+    for (int r = 0; r < rows; ++r) {
+        const uint32_t xb = (uint32_t)in[first + r * stride] << 16;
+        const float q = quant_abs<MODE>(xb, bs, a.fmt);
+        if (out) out[first + r * stride] = (uint16_t)((__float_as_uint(q * bs.scale) | (xb & 0x80000000u)) >> 16);
+        if (CK != CK_NONE) codes_dst[r * codes_stride] = (uint8_t)code_pair<CK>(q, 0.f, xb >> 16);
+    }
+    if (CK != CK_NONE) {
+#pragma unroll 1
+        for (int r = rows; r < pad_to; ++r) codes_dst[r * codes_stride] = 0;
+    }
 }
 
 constexpr int kLastBfThreads = 256;
 constexpr int kLastBfUnroll = 4;
 
-template <int MODE, bool WANT_DQ, bool WANT_CODES>
+template <int MODE, bool WANT_DQ, int CK>
 __global__ void __launch_bounds__(kLastBfThreads)
 mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block) {
+    const int lane_shift = 31 - __clz(lanes_per_block);
     const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll);
     uint4 raw[kLastBfUnroll];
     bool live[kLastBfUnroll];
@@ -352,155 +404,152 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
         for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
         const uint32_t amax = m << 16;
         const FastBlock fb = fast_block(amax, a);
+        if (CK != CK_NONE && live[u] && (threadIdx.x & (lanes_per_block - 1)) == 0)
+            a.scales[scale_index_last(a, (uint32_t)(v >> lane_shift))] = (uint8_t)fb.E;
+        if (!fb.ok) {
+            if (live[u])
+                bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, amax,
+                                          CK != CK_NONE ? a.codes + v * 8 : nullptr, 1, 8);
+            continue;
+        }
+        const uint32_t mp = (__float_as_uint(fb.maxn) >> 16) * 0x10001u;
         uint32_t o[4];
         float q[8];
-        if (fb.ok) {
-            const uint32_t mp = (__float_as_uint(fb.maxn) >> 16) * 0x10001u;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) o[i] = quant_pair_bf16<MODE>(w[i], fb.cmin, fb.cmin, mp, a.fmt, q[2 * i], q[2 * i + 1]);
-            if (WANT_CODES) {
-                const float inv = inv_pow2_from_field(amax == 0 ? 127 : fb.E);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) q[i] = fminf(q[i], fb.maxn) * inv;
-            }
-        } else {
-            const BlockScale bs = block_scale(amax, a);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t lo = quant_slow_bits<MODE>(w[i] << 16, bs, a.fmt, q[2 * i]);
-                const uint32_t hi = quant_slow_bits<MODE>(w[i] & 0xffff0000u, bs, a.fmt, q[2 * i + 1]);
-                o[i] = __byte_perm(lo, hi, 0x7632);
-            }
-        }
+        for (int i = 0; i < 4; ++i) o[i] = quant_pair_bf16<MODE>(w[i], fb.cmin, fb.cmin, mp, a.fmt, q[2 * i], q[2 * i + 1]);
         if (!live[u]) continue;
         if (WANT_DQ) reinterpret_cast<uint4*>(a.out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
-        if (WANT_CODES) {
+        if (CK != CK_NONE) {
             uint32_t c[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-                c[i] = code_pair(q[4 * i], q[4 * i + 1], w[2 * i], a.fmt) |
-                       (code_pair(q[4 * i + 2], q[4 * i + 3], w[2 * i + 1], a.fmt) << 16);
+                c[i] = code_pair<CK>(fminf(q[4 * i], fb.maxn) * fb.inv, fminf(q[4 * i + 1], fb.maxn) * fb.inv, w[2 * i]) |
+                       (code_pair<CK>(fminf(q[4 * i + 2], fb.maxn) * fb.inv, fminf(q[4 * i + 3], fb.maxn) * fb.inv, w[2 * i + 1]) << 16);
             reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
-            if ((threadIdx.x & (lanes_per_block - 1)) == 0) {
-                const int64_t blk = v / lanes_per_block;
-                a.scales[scale_index(a, blk / a.nblk, blk % a.nblk, 0)] = (uint8_t)fb.E;
-            }
         }
     }
 }
 
 constexpr int kStrBfThreads = 128;
 
-template <int MODE, bool WANT_DQ, bool WANT_CODES>
+// TRANSPOSED (only with codes): codes and scales are written with the blocked axis innermost,
+// and a thread walks four consecutive blocks of its columns so that its stores to one output
+// row are 128 contiguous bytes and (in the GEMM scale layout) one 32-bit word of scales.
+template <int MODE, bool WANT_DQ, int CK, bool TRANSPOSED>
 __global__ void __launch_bounds__(kStrBfThreads)
-mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles) {
+mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nbgrp) {
+    constexpr int kBlocksPerThread = TRANSPOSED ? 4 : 1;
     const int64_t t = blockIdx.x;
     const int64_t ct = t % col_tiles;
     const int64_t pb = t / col_tiles;
-    const int64_t b = pb % a.nblk;
-    const int64_t p = pb / a.nblk;
+    const int64_t bg = pb % nbgrp;
+    const int64_t p = pb / nbgrp;
     const int64_t col = ct * (kStrBfThreads * 4) + (int64_t)threadIdx.x * 4;
     if (col >= a.post) return;
-    const int64_t row0 = b * a.block;
-    const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
-    const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
     const uint16_t* in = reinterpret_cast<const uint16_t*>(a.in);
-    uint2 raw[kMaxRows];
-#pragma unroll
-    for (int r = 0; r < kMaxRows; ++r)
-        raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
-    uint32_t m0 = 0, m1 = 0;
-#pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) {
-        m0 = vmax_u16x2(m0, raw[r].x & 0x7fff7fffu);
-        m1 = vmax_u16x2(m1, raw[r].y & 0x7fff7fffu);
-    }
-    const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
-    FastBlock fb[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
-    const bool ok = fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
-    if (WANT_CODES) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
-    }
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
-    uint32_t tc[4][kMaxRows / 4];          // transposed codes: [column][4 rows per word]
-    if (ok) {
-        const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
-        const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
-        float inv[4];
-        if (WANT_CODES) {
+    const int64_t padded = a.nblk * a.block;
+    uint32_t sf_word[4] = {0, 0, 0, 0};
+#pragma unroll 1
+    for (int bb = 0; bb < kBlocksPerThread; ++bb) {
+        const int64_t b = bg * kBlocksPerThread + bb;
+        if (b >= a.nblk) break;
+        const int64_t row0 = b * a.block;
+        const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
+        const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
+        uint2 raw[kMaxRows];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) inv[i] = inv_pow2_from_field(amax[i] == 0 ? 127 : fb[i].E);
-        }
-#pragma unroll
-        for (int r = 0; r < kMaxRows; ++r) {
-            float q[4];
-            const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
-            const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
-            if (WANT_DQ && r < rows)
-                *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
-            if (WANT_CODES) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) q[i] = fminf(q[i], fb[i].maxn) * inv[i];
-                const uint32_t c01 = code_pair(q[0], q[1], raw[r].x, a.fmt);
-                const uint32_t c23 = code_pair(q[2], q[3], raw[r].y, a.fmt);
-                if (a.transposed) {
-                    const int sh = 8 * (r & 3);
-                    if ((r & 3) == 0) { tc[0][r >> 2] = 0; tc[1][r >> 2] = 0; tc[2][r >> 2] = 0; tc[3][r >> 2] = 0; }
-                    tc[0][r >> 2] |= (c01 & 0xffu) << sh;
-                    tc[1][r >> 2] |= (c01 >> 8) << sh;
-                    tc[2][r >> 2] |= (c23 & 0xffu) << sh;
-                    tc[3][r >> 2] |= (c23 >> 8) << sh;
-                } else if (r < rows) {
-                    *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01 | (c23 << 16);
-                }
-            }
-        }
-    } else {
-        BlockScale bs[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) bs[i] = block_scale(amax[i], a);
+        for (int r = 0; r < kMaxRows; ++r)
+            raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
+        uint32_t m0 = 0, m1 = 0;
 #pragma unroll
         for (int r = 0; r < kMaxRows; ++r) {
-            float q[4];
-            const uint32_t l0 = quant_slow_bits<MODE>(raw[r].x << 16, bs[0], a.fmt, q[0]);
-            const uint32_t h0 = quant_slow_bits<MODE>(raw[r].x & 0xffff0000u, bs[1], a.fmt, q[1]);
-            const uint32_t l1 = quant_slow_bits<MODE>(raw[r].y << 16, bs[2], a.fmt, q[2]);
-            const uint32_t h1 = quant_slow_bits<MODE>(raw[r].y & 0xffff0000u, bs[3], a.fmt, q[3]);
-            if (WANT_DQ && r < rows)
-                *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) =
-                    make_uint2(__byte_perm(l0, h0, 0x7632), __byte_perm(l1, h1, 0x7632));
-            if (WANT_CODES) {
-                const uint32_t c01 = code_pair(q[0], q[1], raw[r].x, a.fmt);
-                const uint32_t c23 = code_pair(q[2], q[3], raw[r].y, a.fmt);
-                if (a.transposed) {
-                    const int sh = 8 * (r & 3);
-                    if ((r & 3) == 0) { tc[0][r >> 2] = 0; tc[1][r >> 2] = 0; tc[2][r >> 2] = 0; tc[3][r >> 2] = 0; }
-                    tc[0][r >> 2] |= (c01 & 0xffu) << sh;
-                    tc[1][r >> 2] |= (c01 >> 8) << sh;
-                    tc[2][r >> 2] |= (c23 & 0xffu) << sh;
-                    tc[3][r >> 2] |= (c23 >> 8) << sh;
-                } else if (r < rows) {
-                    *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01 | (c23 << 16);
-                }
-            }
+            m0 = vmax_u16x2(m0, raw[r].x & 0x7fff7fffu);
+            m1 = vmax_u16x2(m1, raw[r].y & 0x7fff7fffu);
         }
-    }
-    if (WANT_CODES && a.transposed) {
-        const int64_t padded = a.nblk * a.block;
+        const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
+        FastBlock fb[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint8_t* dst = a.codes + (p * a.post + col + i) * padded + row0;
-            if (a.block == kMaxRows) {
-                reinterpret_cast<uint4*>(dst)[0] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
-                reinterpret_cast<uint4*>(dst)[1] = make_uint4(tc[i][4], tc[i][5], tc[i][6], tc[i][7]);
+        for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
+        if (CK != CK_NONE) {
+            if (TRANSPOSED && a.sf_gemm) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sf_word[i] |= (uint32_t)(fb[i].E & 0xff) << (8 * bb);
             } else {
 #pragma unroll
-                for (int r = 0; r < kMaxRows; ++r)
-                    if (r < a.block) dst[r] = (uint8_t)(tc[i][r >> 2] >> (8 * (r & 3)));
+                for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
             }
+        }
+        if (!(fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok)) {
+#pragma unroll 1
+            for (int i = 0; i < 4; ++i) {
+                uint8_t* cd = nullptr;
+                int64_t cs = 0;
+                if (CK != CK_NONE) {
+                    if (TRANSPOSED) { cd = a.codes + (p * a.post + col + i) * padded + row0; cs = 1; }
+                    else { cd = a.codes + base + i; cs = a.post; }
+                }
+                const uint32_t mm = (i & 2) ? m1 : m0;
+                const uint32_t am = (i & 1) ? (mm & 0xffff0000u) : (mm << 16);
+                bf16_block_slow<MODE, CK>(a, in, base + i, a.post, rows, am, cd, cs, TRANSPOSED ? a.block : rows);
+            }
+            continue;
+        }
+        const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
+        const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
+        const float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
+        uint32_t tc[4][kMaxRows / 4];          // transposed codes: [column][4 rows per word]
+#pragma unroll
+        for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
+            uint32_t c01[4], c23[4];
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+                const int r = r4 * 4 + rr;
+                float q[4];
+                const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
+                const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
+                if (WANT_DQ && r < rows)
+                    *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
+                if (CK != CK_NONE) {
+                    c01[rr] = code_pair<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1], raw[r].x);
+                    c23[rr] = code_pair<CK>(fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].y);
+                    if (!TRANSPOSED && r < rows)
+                        *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01[rr] | (c23[rr] << 16);
+                }
+            }
+            if (CK != CK_NONE && TRANSPOSED) {
+                // 4 rows x 2 columns of code bytes -> one word per column (rows innermost)
+                const uint32_t t0 = __byte_perm(c01[0], c01[1], 0x5140), t1 = __byte_perm(c01[2], c01[3], 0x5140);
+                const uint32_t u0 = __byte_perm(c23[0], c23[1], 0x5140), u1 = __byte_perm(c23[2], c23[3], 0x5140);
+                tc[0][r4] = __byte_perm(t0, t1, 0x5410);
+                tc[1][r4] = __byte_perm(t0, t1, 0x7632);
+                tc[2][r4] = __byte_perm(u0, u1, 0x5410);
+                tc[3][r4] = __byte_perm(u0, u1, 0x7632);
+            }
+        }
+        if (CK != CK_NONE && TRANSPOSED) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint8_t* dst = a.codes + (p * a.post + col + i) * padded + row0;
+                if (a.block == kMaxRows) {
+                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
+                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(tc[i][4], tc[i][5], tc[i][6], tc[i][7]);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kMaxRows; ++r)
+                        if (r < a.block) dst[r] = (uint8_t)(tc[i][r >> 2] >> (8 * (r & 3)));
+                }
+            }
+        }
+    }
+    if (CK != CK_NONE && TRANSPOSED && a.sf_gemm) {
+        const int64_t b0 = bg * kBlocksPerThread;
+        const int nb = (int)min((int64_t)kBlocksPerThread, a.nblk - b0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint8_t* dst = a.scales + scale_index(a, p, b0, col + i);
+            if (nb == 4) *reinterpret_cast<uint32_t*>(dst) = sf_word[i];
+            else for (int k = 0; k < nb; ++k) dst[k] = (uint8_t)(sf_word[i] >> (8 * k));
         }
     }
 }
@@ -577,21 +626,40 @@ static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream
     const int64_t tile = (int64_t)kLastBfThreads * kLastBfUnroll;
     const int64_t grid = (nvec + tile - 1) / tile;
     if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
-    if (a.out && a.codes) mx_lastaxis_bf16_kernel<MODE, true, true><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else if (a.codes) mx_lastaxis_bf16_kernel<MODE, false, true><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else mx_lastaxis_bf16_kernel<MODE, true, false><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    const unsigned g = (unsigned)grid;
+    const bool e5 = a.fmt.ebits == 5;
+    if (!a.codes) mx_lastaxis_bf16_kernel<MODE, true, CK_NONE><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else if (a.out && e5) mx_lastaxis_bf16_kernel<MODE, true, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else if (a.out) mx_lastaxis_bf16_kernel<MODE, true, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else if (e5) mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    else mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    return check_launch();
+}
+
+template <int MODE, bool WANT_DQ, int CK, bool TR>
+static int launch_strided_bf16_one(const MxArgs& a, cudaStream_t st) {
+    const int64_t col_tiles = (a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
+    const int64_t nbgrp = TR ? (a.nblk + 3) / 4 : a.nblk;
+    const int64_t grid = col_tiles * a.pre * nbgrp;
+    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+    mx_strided_bf16_kernel<MODE, WANT_DQ, CK, TR><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles, nbgrp);
     return check_launch();
 }
 
 template <int MODE>
 static int launch_strided_bf16(const MxArgs& a, cudaStream_t st) {
-    const int64_t col_tiles = (a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
-    const int64_t grid = col_tiles * a.pre * a.nblk;
-    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
-    if (a.out && a.codes) mx_strided_bf16_kernel<MODE, true, true><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
-    else if (a.codes) mx_strided_bf16_kernel<MODE, false, true><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
-    else mx_strided_bf16_kernel<MODE, true, false><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles);
-    return check_launch();
+    const bool e5 = a.fmt.ebits == 5;
+    if (!a.codes) return launch_strided_bf16_one<MODE, true, CK_NONE, false>(a, st);
+    if (a.transposed) {
+        if (a.out) return e5 ? launch_strided_bf16_one<MODE, true, CK_E5M2, true>(a, st)
+                             : launch_strided_bf16_one<MODE, true, CK_E4M3, true>(a, st);
+        return e5 ? launch_strided_bf16_one<MODE, false, CK_E5M2, true>(a, st)
+                  : launch_strided_bf16_one<MODE, false, CK_E4M3, true>(a, st);
+    }
+    if (a.out) return e5 ? launch_strided_bf16_one<MODE, true, CK_E5M2, false>(a, st)
+                         : launch_strided_bf16_one<MODE, true, CK_E4M3, false>(a, st);
+    return e5 ? launch_strided_bf16_one<MODE, false, CK_E5M2, false>(a, st)
+              : launch_strided_bf16_one<MODE, false, CK_E4M3, false>(a, st);
 }
 
 template <int DT>
@@ -606,10 +674,10 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
     const bool ptrs8 = aligned8(a.in) && (!a.out || aligned8(a.out)) && (!a.codes || aligned8(a.codes));
 
     if (fast_math && a.post == 1 && pow2 && a.block >= N16 && a.block <= 32 * N16 &&
-        a.axis_len % a.block == 0 && ptrs16 && !a.transposed) {
+        a.axis_len % a.block == 0 && ptrs16 && !a.transposed && total / a.block <= 0xffffffffLL) {
         const int lanes = a.block / N16;
         const int64_t nvec = total / N16;
-        if (DT == DT_BF16 && P <= 8) {
+        if (DT == DT_BF16 && P <= 8 && (!a.codes || a.fmt.ebits != 0)) {
             switch (a.mode) {
                 case RN_AWAY: return launch_last_bf16<RN_AWAY>(a, nvec, lanes, st);
                 case RZ:      return launch_last_bf16<RZ>(a, nvec, lanes, st);
@@ -623,7 +691,7 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
         }
     }
     if (fast_math && a.post > 1 && a.block <= kMaxRows && a.post % N8 == 0 && ptrs8) {
-        if (DT == DT_BF16 && P <= 8 && (!a.codes || !a.transposed || aligned16(a.codes))) {
+        if (DT == DT_BF16 && P <= 8 && (!a.codes || (a.fmt.ebits != 0 && (!a.transposed || aligned16(a.codes)) && (!a.sf_gemm || !a.scales || (reinterpret_cast<uintptr_t>(a.scales) & 3u) == 0)))) {
             switch (a.mode) {
                 case RN_AWAY: return launch_strided_bf16<RN_AWAY>(a, st);
                 case RZ:      return launch_strided_bf16<RZ>(a, st);

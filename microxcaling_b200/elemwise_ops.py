@@ -122,6 +122,9 @@ def quantize_elemwise_op(A, mx_specs, round=None):
         return A.to(torch.bfloat16)
     if mx_specs["bfloat"] > 0 and mx_specs["fp"] > 0:
         raise ValueError("Cannot set both [bfloat] and [fp] in mx_specs.")
+    if A.dtype == torch.bfloat16 and A.is_cuda and 16 <= mx_specs["bfloat"] and mx_specs["bfloat_subnorms"] \
+            and round in ("nearest", "floor", "even"):
+        return A        # every bfloat16 value is on the bfloatX grid (X >= 16): nothing to round
     if mx_specs["bfloat"] > 9:
         return _quantize_bfloat(A, bfloat=mx_specs["bfloat"], round=round, custom_cuda=mx_specs["custom_cuda"],
                                 allow_denorm=mx_specs["bfloat_subnorms"])
