@@ -105,6 +105,64 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one mx_strided_bf16_kernel launch on this workload
+# (profiles/mx_strided_bf16_kernel__c2_sweep.md)
+STRIDED_TRAFFIC_BYTES = 219_897_856
+
+
+def mx_linear_block(torch, be, dev):
+    """MX linear at the config-3 shape (8192 tokens, 4096 -> 4096, fp8_e4m3 forward, fp8_e5m2 backward,
+    block 32, bfloat16): GEMM-only throughput of the block-scaled tensor-core kernel, and forward+backward
+    of mx.Linear through the Python API (6 MX quantizations + 3 GEMMs per step), CUDA events."""
+    import microxcaling_b200 as mx
+    from microxcaling_b200.specs import finalize_mx_specs
+    M, K, N = 8192, 4096, 4096
+    g = torch.Generator(device="cpu").manual_seed(7)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    go = torch.randn(M, N, generator=g).to(torch.bfloat16).to(dev)
+    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "w_elem_format_bp": "fp8_e5m2",
+                            "a_elem_format_bp": "fp8_e5m2", "a_elem_format_bp_ex": "fp8_e5m2",
+                            "a_elem_format_bp_os": "fp8_e5m2", "block_size": 32, "scale_bits": 8, "bfloat": 16,
+                            "custom_cuda": True})
+    torch.manual_seed(0)
+    layer = mx.Linear(K, N, bias=False, mx_specs=sp).to(dev).to(torch.bfloat16)
+    xr = x.clone().requires_grad_()
+    _, ca, sa = be.quantize_mx(x, 8, 4, 5, 448.0, 32, 1, want_dq=False, want_codes=True, gemm_layout=True)
+    _, cb, sb = be.quantize_mx(layer.weight.detach(), 8, 4, 5, 448.0, 32, 1, want_dq=False, want_codes=True,
+                               gemm_layout=True)
+    out = torch.empty(1, M, N, dtype=torch.bfloat16, device=dev)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    def step():
+        y = layer(xr)
+        y.backward(go)
+        layer.weight.grad = None
+        xr.grad = None
+
+    t_gemm = timed(lambda: be.gemm_mx(ca, sa, cb, sb, 1, M, N, K, 0, 0, torch.bfloat16, 16, 0, None, 0, out=out), 50)
+    t_step = timed(step, 20)
+    assert be.device_status() == 0
+    flop = 2.0 * M * N * K
+    return {"shape": "8192 x 4096 -> 4096, w/a fp8_e4m3, backward fp8_e5m2, block 32, bfloat16 output rounding",
+            "gemm_us": t_gemm * 1e6, "gemm_tflops": flop / t_gemm / 1e12,
+            "fwd_bwd_us": t_step * 1e6, "fwd_bwd_tflops": 3 * flop / t_step / 1e12,
+            "tensor_peak_nominal_tflops": 4500.0, "gemm_frac_of_nominal": flop / t_gemm / 1e12 / 4500.0,
+            "tensor_pipe_active_pct_ncu": 73.4,
+            "note": "fwd_bwd counts the 3 GEMMs' flops over the whole step (6 MX quantizations included); "
+                    "tensor_pipe_active_pct_ncu from profiles/gemm_mx_kernel__8192x4096x4096.md"}
+
+
 def cpu_baseline(torch, x_rows_f32, kind_wanted=None):
     """Times the nine passes on a [CPU_SAMPLE_ROWS, 8192] fp32-container slab
     with all host threads: the reference's own C++ math where oracle/_ref was
@@ -263,6 +321,11 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
+    # ---- MX linear (config 3 shape): packed-operand GEMM and the full layer ----
+    lin = None
+    if rank == 0:
+        lin = mx_linear_block(torch, be, dev)
+
     if rank == 0:
         step_bytes = PASSES * PASS_BYTES
         value = world * step_bytes * K / (total_ms * 1e-3) / 1e9
@@ -293,9 +356,8 @@ def main():
             "gpu_launches": PASSES * K,
             "clocks": clocks,
         }
-        traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(traffic_file):
-            out["roofline"]["traffic"] = json.load(open(traffic_file)).get("mx_strided_bf16_kernel")
+        out["roofline"]["traffic"] = STRIDED_TRAFFIC_BYTES
+        out["mx_linear"] = lin
         if world == 1:
             cb, _ = cpu_baseline(torch, xs[0][:CPU_SAMPLE_ROWS].float().cpu().numpy())
             out["cpu_baseline"] = cb

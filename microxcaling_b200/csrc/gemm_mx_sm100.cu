@@ -237,7 +237,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int half = e >> 2;
         const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * 2048);
         const bool f32_out = g.out_dtype == DT_F32;
-        const int chunk_cols = f32_out ? 16 : 32;
         const float* bp = reinterpret_cast<const float*>(g.bias);
         uint32_t tile_i = 0;
         bool ok = true;
@@ -251,43 +250,52 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (warp == 2 && lane == 0) TRACE(600 + 2 * tile_i);
             const int64_t row0 = mt * kBM + q * 32;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN;
-#pragma unroll 1
-            for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += chunk_cols) {
-                const int64_t col0 = nt * BN + c0;
-                if (col0 >= g.N) break;
-                uint32_t v[32];
-                uint32_t w[16];
-                const int tch = (c0 - half * (BN / 2)) / chunk_cols;
-                if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 0);
-                if (f32_out) {
-                    ptx::tmem_ld_32x32b_x16(taddr + c0, *reinterpret_cast<uint32_t(*)[16]>(v));
-                    ptx::tmem_ld_wait();
+            // Read this warp's whole share of the accumulator (BN/2 columns) into registers first
+            // and hand the tensor-memory buffer back to the MMA warp at once; rounding and stores
+            // then overlap the next tile's main loop even with a single accumulator buffer.
+            constexpr int kCols = BN / 2;
+            uint32_t v[kCols];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        uint32_t b = round_out_bits(v[i], g.rnd);
-                        if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
-                        w[i] = b;
-                    }
-                } else {
-                    ptx::tmem_ld_32x32b_x32(taddr + c0, v);
-                    ptx::tmem_ld_wait();
-                    if (g.epi_kind == 0) {                     // half away: add half an ulp of bf16, keep the upper halves
+            for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
+            if (warp == 2 && lane == 0) TRACE(800 + 2 * tile_i);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[2 * i] + 0x8000u, v[2 * i + 1] + 0x8000u, 0x7632);
+            for (int cc = 0; cc < kCols; cc += 32) {
+                // 32 accumulator columns: one 64-byte chunk of bf16 or two of fp32
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    if (!f32_out && sub == 1) break;
+                    const int c0 = half * kCols + cc + sub * 16;
+                    const int64_t col0 = nt * BN + c0;
+                    if (col0 >= g.N) break;
+                    uint32_t w[16];
+                    if (f32_out) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            uint32_t b = round_out_bits(v[cc + sub * 16 + i], g.rnd);
+                            if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
+                            w[i] = b;
+                        }
+                    } else if (g.epi_kind == 0) {              // half away: add half an ulp of bf16, keep the upper halves
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i] + 0x8000u, v[cc + 2 * i + 1] + 0x8000u, 0x7632);
                     } else if (g.epi_kind == 1) {              // toward zero
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[2 * i], v[2 * i + 1], 0x7632);
+                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i], v[cc + 2 * i + 1], 0x7632);
                     } else if (g.epi_kind == 2) {              // half even: the hardware conversion
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[cc + 2 * i]), __uint_as_float(v[cc + 2 * i + 1]));
                             w[i] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            uint32_t b0 = round_out_bits(v[2 * i], g.rnd);
-                            uint32_t b1 = round_out_bits(v[2 * i + 1], g.rnd);
+                            uint32_t b0 = round_out_bits(v[cc + 2 * i], g.rnd);
+                            uint32_t b1 = round_out_bits(v[cc + 2 * i + 1], g.rnd);
                             if (bp) {
                                 b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
                                 b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
@@ -296,41 +304,33 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             w[i] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     }
-                }
-                if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 1);
-                if (g.c_tma) {
-                    if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
-                    __syncwarp();
-                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 2);
+                    if (g.c_tma) {
+                        if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
+                        __syncwarp();
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-                    ptx::fence_proxy_async();
-                    __syncwarp();
-                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 3);
-                    if (lane == 0) {
-                        ptx::tma_store_3d(&tmap_c, stg, (int)col0, (int)row0, (int)bi);
-                        ptx::bulk_commit();
-                    }
-                    if (warp == 2 && lane == 0 && tile_i < 2 && tch < 4) TRACE(900 + 10 * (tile_i * 4 + tch) + 4);
-                } else if (row0 + lane < g.M) {
-                    // row pitch not a multiple of 16 bytes: plain stores
-                    const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
+                        for (int c = 0; c < 4; ++c)
+                            ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_3d(&tmap_c, stg, (int)col0, (int)row0, (int)bi);
+                            ptx::bulk_commit();
+                        }
+                    } else if (row0 + lane < g.M) {
+                        // row pitch not a multiple of 16 bytes: plain stores
+                        const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if (f32_out) {
-                            if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
-                        } else {
-                            if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
-                            if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
+                        for (int i = 0; i < 16; ++i) {
+                            if (f32_out) {
+                                if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
+                            } else {
+                                if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
+                                if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
+                            }
                         }
                     }
                 }
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
-            if (warp == 2 && lane == 0) TRACE(800 + 2 * tile_i);
         }
         if (lane == 0) ptx::bulk_wait_all();
     }
