@@ -109,6 +109,89 @@ __global__ void ew_scalar_kernel(const EwArgs a, const int64_t first, const int6
     store1<OUT_DT>(a.out, i, __uint_as_float(ew_one<IN_DT, OUT_DT, PATH, MODE>(u, a, i)));
 }
 
+// bf16 -> bf16 for bfloat-family targets: the rounding acts on the bf16 bit
+// pattern itself (drop16 = low mantissa bits removed, 0 = nothing to round), two
+// elements per 32-bit operation.  Vectors that hold Inf/NaN (or subnormals when
+// those are flushed) take the per-element routine.
+__device__ __forceinline__ uint32_t vmaxu2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t vminu2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+constexpr int kEwBfUnroll = 4;
+
+template <int MODE>
+__global__ void __launch_bounds__(kEwThreads)
+ew_bf16_pairs_kernel(const EwArgs a, const int64_t nvec, const uint32_t drop16, const uint32_t cap16) {
+    const int64_t base = (int64_t)blockIdx.x * (kEwThreads * kEwBfUnroll);
+    uint4 raw[kEwBfUnroll];
+    bool live[kEwBfUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwBfUnroll; ++u) {
+        const int64_t v = base + (int64_t)u * kEwThreads + threadIdx.x;
+        live[u] = v < nvec;
+        raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in) + v) : make_uint4(0, 0, 0, 0);
+    }
+    const uint32_t mask = ((1u << drop16) - 1u) * 0x10001u;
+    const uint32_t half = drop16 ? (1u << (drop16 - 1)) * 0x10001u : 0u;
+    const uint32_t cap = cap16 * 0x10001u;
+#pragma unroll
+    for (int u = 0; u < kEwBfUnroll; ++u) {
+        if (!live[u]) continue;
+        const int64_t v = base + (int64_t)u * kEwThreads + threadIdx.x;
+        uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        uint32_t mag[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mag[i] = w[i] & 0x7fff7fffu;
+        const uint32_t mx = vmaxu2(vmaxu2(mag[0], mag[1]), vmaxu2(mag[2], mag[3]));
+        const bool special = (mx & 0xffffu) >= 0x7f80u || (mx >> 16) >= 0x7f80u || !a.allow_denorm;
+        uint32_t o[4];
+        if (!special) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t r = mag[i];
+                if (MODE == RN_AWAY) r += half;
+                else if (MODE == RN_EVEN) r += (half - (drop16 ? 0x10001u : 0u)) + ((mag[i] >> drop16) & (drop16 ? 0x10001u : 0u));
+                r &= ~mask;
+                r = vminu2(r, cap);                     // overflow -> Inf pattern, or max_norm when saturating
+                o[i] = r | (w[i] & 0x80008000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t lo = round_bf_family<MODE>(w[i] << 16, a);
+                const uint32_t hi = round_bf_family<MODE>(w[i] & 0xffff0000u, a);
+                o[i] = __byte_perm(lo, hi, 0x7632);
+            }
+        }
+        reinterpret_cast<uint4*>(a.out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+template <int MODE>
+static int launch_ew_bf16_pairs(const EwArgs& a, cudaStream_t st) {
+    // bits = P + 1 with P significand bits; bf16 carries 8, so 8 - P low bits go
+    const int P = a.bits - 1;
+    const uint32_t drop16 = P >= 8 ? 0u : (uint32_t)(8 - P);
+    const uint32_t cap16 = a.saturate ? (a.max_bits >> 16) : 0x7f80u;
+    const int64_t nvec = a.n / 8;
+    if (nvec > 0) {
+        const int64_t tile = (int64_t)kEwThreads * kEwBfUnroll;
+        const int64_t grid = (nvec + tile - 1) / tile;
+        if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+        ew_bf16_pairs_kernel<MODE><<<(unsigned)grid, kEwThreads, 0, st>>>(a, nvec, drop16, cap16);
+    }
+    const int64_t first = nvec * 8;
+    if (first < a.n) ew_scalar_kernel<DT_BF16, DT_BF16, 0, MODE><<<1, 128, 0, st>>>(a, first, a.n);
+    return check_launch();
+}
+
 template <int IN_DT, int OUT_DT, int PATH, int MODE>
 static int launch_ew(const EwArgs& a, cudaStream_t st) {
     const bool vec_ok = aligned16(a.in) && aligned16(a.out);
@@ -130,6 +213,18 @@ static int launch_ew(const EwArgs& a, cudaStream_t st) {
 
 template <int IN_DT, int OUT_DT>
 static int dispatch_path(const EwArgs& a, cudaStream_t st) {
+    // the packed bf16 path takes "above max_norm" to mean "rounded past the top of the grid", which
+    // holds when max_norm is the largest finite value of the format (what _get_max_norm gives)
+    const int p_bits = a.bits - 1;
+    const uint32_t grid_top = 0x7f7f0000u & ~(((p_bits >= 8 ? 0u : (1u << (8 - p_bits)) - 1u)) << 16);
+    if (IN_DT == DT_BF16 && OUT_DT == DT_BF16 && a.exp_bits == 8 && a.mode <= RN_EVEN && a.bits >= 2 &&
+        a.max_bits == grid_top && aligned16(a.in) && aligned16(a.out)) {
+        switch (a.mode) {
+            case RN_AWAY: return launch_ew_bf16_pairs<RN_AWAY>(a, st);
+            case RZ:      return launch_ew_bf16_pairs<RZ>(a, st);
+            default:      return launch_ew_bf16_pairs<RN_EVEN>(a, st);
+        }
+    }
     if (a.exp_bits == 8 && a.mode <= RN_EVEN) {
         switch (a.mode) {
             case RN_AWAY: return launch_ew<IN_DT, OUT_DT, 0, RN_AWAY>(a, st);
