@@ -163,6 +163,50 @@ def mx_linear_block(torch, be, dev):
                     "tensor_pipe_active_pct_ncu from profiles/gemm_mx_kernel__8192x4096x4096.md"}
 
 
+def mx_ffn_block(torch, dist, dev, rank, world):
+    """Forward of the Llama-style FFN block of config 5 (hidden 8192, intermediate 28672, 16384 tokens,
+    w fp4_e2m1, a fp8_e4m3, block 32, bfloat16), tensor-parallel over the ranks: column-parallel gate/up,
+    row-parallel down, packed activations all-gathered, fp32 partials reduce-scattered (NCCL).  Total
+    work is fixed (strong scaling); the time is the max over ranks."""
+    from microxcaling_b200.specs import finalize_mx_specs
+    from microxcaling_b200.tp import TensorParallelFFN
+    H, I, T = 8192, 28672, 16384
+    if I % (128 * world) or T % (128 * world):
+        return {"skipped": "shape does not split over %d ranks" % world}
+    sp = finalize_mx_specs({"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32,
+                            "scale_bits": 8, "bfloat": 16, "custom_cuda": True})
+    torch.manual_seed(100 + rank)
+    ffn = TensorParallelFFN(H, I, sp, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for w in (ffn.w_gate, ffn.w_up, ffn.w_down):
+            w.copy_((torch.rand(w.shape, device=dev) * 2 - 1) * (1.0 / w.shape[1]) ** 0.5)
+    x = torch.randn(T // world, H, device=dev, dtype=torch.bfloat16)
+    for _ in range(4):
+        y = ffn(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    iters = 10
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        y = ffn(x)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / iters
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    flop = 3 * 2.0 * T * H * I
+    del ffn, x, y
+    torch.cuda.empty_cache()
+    return {"shape": "16384 tokens, hidden 8192, intermediate 28672, SwiGLU + RMSNorm, w fp4_e2m1 / a fp8_e4m3",
+            "parallelism": "tp%d (column-parallel gate/up, row-parallel down, NCCL all-gather of packed "
+                           "activations + reduce-scatter of fp32 partials)" % world,
+            "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "scaling": "strong"}
+
+
 def cpu_baseline(torch, x_rows_f32, kind_wanted=None):
     """Times the nine passes on a [CPU_SAMPLE_ROWS, 8192] fp32-container slab
     with all host threads: the reference's own C++ math where oracle/_ref was
@@ -326,6 +370,9 @@ def main():
     if rank == 0:
         lin = mx_linear_block(torch, be, dev)
 
+    # ---- tensor-parallel MX FFN (config 5 shape), all ranks ----
+    ffn = mx_ffn_block(torch, dist, dev, rank, world)
+
     if rank == 0:
         step_bytes = PASSES * PASS_BYTES
         value = world * step_bytes * K / (total_ms * 1e-3) / 1e9
@@ -358,6 +405,7 @@ def main():
         }
         out["roofline"]["traffic"] = STRIDED_TRAFFIC_BYTES
         out["mx_linear"] = lin
+        out["mx_ffn"] = ffn
         if world == 1:
             cb, _ = cpu_baseline(torch, xs[0][:CPU_SAMPLE_ROWS].float().cpu().numpy())
             out["cpu_baseline"] = cb

@@ -1,0 +1,159 @@
+"""Tensor-parallel MX feed-forward block (Llama style: RMSNorm -> gate/up ->
+SiLU(gate) * up -> down) over the GPUs of one node.
+
+The reference has no distributed code; this module adds the one exchange pattern
+its FFN admits without changing results beyond fp32 accumulation order:
+
+  * tokens are sharded across ranks for everything that is token-local
+    (RMSNorm, MX quantization of the block input along `hidden`);
+  * the packed input (one code byte per element + E8M0 scales) is all-gathered,
+    4x fewer bytes than fp32 values;
+  * gate/up are column-parallel: each rank owns `intermediate / p` output
+    features, so every output element is a complete dot product and equals the
+    single-GPU value bit for bit;
+  * SiLU and the product are elementwise on the local columns;
+  * down is row-parallel: each rank contracts over its slice of `intermediate`
+    (a multiple of 32, so MX blocks never straddle ranks), the fp32 partial sums
+    are reduce-scattered over tokens and rounded to bfloat once, after the sum.
+
+On CUDA tensors the GEMMs run on packed operands through libmxq; on CPU tensors
+(used by the gloo tests of this logic) the same steps run on fake-quantized
+values with torch's GEMM.  `world_size == 1` skips the collectives.
+"""
+import torch
+import torch.distributed as dist
+
+from . import activations, layernorm, simd_ops
+from ._mxgemm import _MODE, _fast_ok, _fmt, _pack, mx_gemm
+from .elemwise_ops import quantize_elemwise_op
+from .formats import _get_format_params
+from .specs import apply_mx_specs
+
+
+def shard_bounds(n, rank, world, multiple=1):
+    """[lo, hi) of rank's contiguous shard of n items; n must split evenly into
+    shards that are multiples of `multiple`."""
+    if n % world != 0 or (n // world) % multiple != 0:
+        raise ValueError("cannot split %d items over %d ranks in multiples of %d" % (n, world, multiple))
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+class TensorParallelFFN(torch.nn.Module):
+    def __init__(self, hidden, intermediate, mx_specs, group=None, eps=1e-5, device=None, dtype=torch.bfloat16):
+        super().__init__()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.hidden, self.intermediate = hidden, intermediate
+        self.mx_specs = apply_mx_specs(mx_specs)
+        lo, hi = shard_bounds(intermediate, self.rank, self.world, multiple=128)
+        self.cols = (lo, hi)
+        kw = dict(device=device, dtype=dtype)
+        self.norm = layernorm.RMSNorm(hidden, eps=eps, mx_specs=mx_specs).to(**kw)
+        self.w_gate = torch.nn.Parameter(torch.empty(hi - lo, hidden, **kw))
+        self.w_up = torch.nn.Parameter(torch.empty(hi - lo, hidden, **kw))
+        self.w_down = torch.nn.Parameter(torch.empty(hidden, hi - lo, **kw))
+        self._packed = None
+
+    @torch.no_grad()
+    def load_full(self, w_gate, w_up, w_down, norm_weight=None):
+        """Take this rank's shards out of full (unsharded) weight matrices."""
+        lo, hi = self.cols
+        self.w_gate.copy_(w_gate[lo:hi])
+        self.w_up.copy_(w_up[lo:hi])
+        self.w_down.copy_(w_down[:, lo:hi])
+        if norm_weight is not None:
+            self.norm.weight.copy_(norm_weight)
+        self._packed = None
+
+    # ------------------------------------------------------------------ helpers
+    def _fast(self, x):
+        sp = self.mx_specs
+        return _fast_ok(x, self.w_gate, _fmt(sp["a_elem_format"]), _fmt(sp["w_elem_format"]), sp, self.hidden,
+                        sp["round_mx_output"], sp["round_mx_output"], sp["round_output"]) and \
+            (self.cols[1] - self.cols[0]) % 128 == 0
+
+    def _weights_packed(self):
+        if self._packed is None:
+            sp = self.mx_specs
+            rnd = sp["round_mx_output"]
+            wf = _fmt(sp["w_elem_format"])
+            q = lambda w: _pack(quantize_elemwise_op(w.detach(), sp, round=sp["round_weight"]), wf, sp, rnd, True)
+            self._packed = (q(self.w_gate), q(self.w_up), q(self.w_down))
+        return self._packed
+
+    def _all_gather_rows(self, t):
+        if self.world == 1:
+            return t
+        out = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+    def _reduce_scatter_rows(self, t):
+        if self.world == 1:
+            return t
+        out = torch.empty((t.shape[0] // self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.reduce_scatter_tensor(out, t.contiguous(), op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward(self, x_local):
+        """x_local: this rank's [tokens / p, hidden] slice (tokens / p a multiple of 128 when p > 1).
+        Returns the same slice of the block output."""
+        sp = self.mx_specs
+        if x_local.dim() != 2 or x_local.shape[1] != self.hidden:
+            raise ValueError("expected a [tokens, hidden] tensor")
+        if self.world > 1 and x_local.shape[0] % 128 != 0:
+            raise ValueError("the per-rank token count must be a multiple of 128")
+        h = self.norm(x_local)
+        if self._fast(h):
+            return self._forward_packed(h)
+        return self._forward_values(h)
+
+    def _forward_packed(self, h):
+        from . import _backend as be
+        sp = self.mx_specs
+        af = _fmt(sp["a_elem_format"])
+        rnd, out_rnd = sp["round_mx_output"], _MODE[sp["round_output"]]
+        bits = sp["bfloat"] if sp["bfloat"] >= 10 else 0
+        (gc, gs, gk), (uc, us, uk), (dc, ds, dk) = self._weights_packed()
+        h = quantize_elemwise_op(h, sp, round=sp["round_output"])
+        xc, xs, xk = _pack(h, af, sp, rnd, True)                       # local tokens
+        xc, xs = self._all_gather_rows(xc), self._all_gather_rows(xs.view(-1, 512)).view(-1)
+        T = xc.shape[0]
+        Il = self.cols[1] - self.cols[0]
+        gate = be.gemm_mx(xc, xs, gc, gs, 1, T, Il, self.hidden, xk, gk, out_dtype=h.dtype, bfloat_bits=bits,
+                          round_mode=out_rnd)[0]
+        up = be.gemm_mx(xc, xs, uc, us, 1, T, Il, self.hidden, xk, uk, out_dtype=h.dtype, bfloat_bits=bits,
+                        round_mode=out_rnd)[0]
+        act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
+        act = quantize_elemwise_op(act, sp, round=sp["round_output"])
+        ac, as_, ak = _pack(act, af, sp, rnd, True)
+        if self.world == 1:
+            return be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=h.dtype, bfloat_bits=bits,
+                              round_mode=out_rnd)[0]
+        part = be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=torch.float32, bfloat_bits=0,
+                          round_mode=-1)[0]
+        out = self._reduce_scatter_rows(part)
+        out = quantize_elemwise_op(out, sp, round=sp["round_output"])
+        return out.to(h.dtype)
+
+    def _forward_values(self, h):
+        sp = self.mx_specs
+        no_round = sp.copy()
+        no_round["bfloat"], no_round["fp"] = 0, 0
+        af, wf, rnd = sp["a_elem_format"], sp["w_elem_format"], sp["round_mx_output"]
+        h = quantize_elemwise_op(h, sp, round=sp["round_output"])
+        x = self._all_gather_rows(h)
+        qw = lambda w: quantize_elemwise_op(w.detach().to(x.dtype), sp, round=sp["round_weight"])
+        gate = mx_gemm(x, qw(self.w_gate), af, wf, sp, rnd, rnd, sp["round_output"], trans2=True)
+        up = mx_gemm(x, qw(self.w_up), af, wf, sp, rnd, rnd, sp["round_output"], trans2=True)
+        act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
+        act = quantize_elemwise_op(act, sp, round=sp["round_output"])
+        if self.world == 1:
+            return mx_gemm(act, qw(self.w_down), af, wf, sp, rnd, rnd, sp["round_output"], trans2=True)
+        part = mx_gemm(act.float(), qw(self.w_down).float(), af, wf, no_round, rnd, rnd, "nearest", trans2=True)
+        out = self._reduce_scatter_rows(part)
+        return quantize_elemwise_op(out, sp, round=sp["round_output"]).to(h.dtype)
