@@ -340,17 +340,17 @@ def main():
     specs = finalize_mx_specs({"a_elem_format": "fp6_e3m2", "block_size": 32, "scale_bits": 8, "bfloat": 16,
                                "custom_cuda": True})
     hx = xs[0].cpu().pin_memory()
-    hy = torch.empty_like(hx).pin_memory()
 
     def e2e_step():
+        # host tensor in, host tensor out, through the public ops: the library cuts the tensor into
+        # chunks and overlaps H2D, kernel and D2H (mxq_quantize_mx_host / mxq_quantize_elemwise_host)
         for i in range(PASSES):
-            xd = hx.to(dev, non_blocking=True)
             if i < 8:
-                yd = quantize_mx_op(xd, specs, elem_format=MX_FORMATS[i // 2], axes=[0 if i % 2 == 0 else -1],
+                hy = quantize_mx_op(hx, specs, elem_format=MX_FORMATS[i // 2], axes=[0 if i % 2 == 0 else -1],
                                     round="nearest")
             else:
-                yd = _quantize_bfloat(xd, 16, round="even", custom_cuda=True)
-            hy.copy_(yd, non_blocking=True)
+                hy = _quantize_bfloat(hx, 16, round="even", custom_cuda=True)
+            assert not hy.is_cuda
         torch.cuda.synchronize()
 
     e2e_step()

@@ -105,6 +105,28 @@ int mxq_quantize_elemwise(const void* in, void* out, int in_dtype, int out_dtype
                           void* stream);
 
 /*
+ * The two quantizers for tensors in HOST memory (use pinned memory: pageable
+ * memory makes the copies synchronous).  Same arguments as the device entry
+ * points, plus a device workspace of mxq_host_workspace_bytes() bytes
+ * (256-byte aligned).  The tensor is processed in chunks of whole blocks on
+ * three internal streams (created on first use, kept until exit) so that the
+ * host->device copy, the kernel and the device->host copy of different chunks
+ * overlap; the work is ordered after what `stream` holds at the call, and
+ * `stream` waits for it.  The reference's counterpart for host tensors is its
+ * single-threaded C++ loop, quantize_mx_func_cpp / quantize_elemwise_func_cpp
+ * (mx/cpp/funcs.cpp:23-149).  Codes / scales outputs and 'dither' are not
+ * offered here.
+ */
+int mxq_quantize_mx_host(const void* h_in, void* h_out, int dtype, int64_t pre, int64_t axis_len,
+                         int64_t post, int block, int scale_bits, int elem_ebits, int elem_mbits,
+                         float elem_max_norm, int flush_fp32_subnorms, int rmode, void* workspace,
+                         int64_t workspace_bytes, void* stream);
+int mxq_quantize_elemwise_host(const void* h_in, void* h_out, int in_dtype, int out_dtype, int64_t n,
+                               int bits, int exp_bits, float max_norm, int rmode, int saturate_normals,
+                               int allow_denorm, void* workspace, int64_t workspace_bytes, void* stream);
+int64_t mxq_host_workspace_bytes(void);
+
+/*
  * Sum / max over the innermost dimension of an fp32 [rows, inner] matrix into
  * out[rows].  Replace reduce_sum_inner_dim / reduce_max_inner_dim
  * (mx/cpp/funcs.cpp:219-231, mx/cpp/reduce.cu:15-89).  Any inner >= 1 is

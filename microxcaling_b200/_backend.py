@@ -44,6 +44,9 @@ def lib():
         L.mxq_sf_bytes.argtypes = [i64, i64, i64]
         L.mxq_sf_bytes.restype = i64
         L.mxq_device_status.argtypes = [i32]
+        L.mxq_quantize_mx_host.argtypes = [vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32, i32, i32, vp, i64, vp]
+        L.mxq_quantize_elemwise_host.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, i64, vp]
+        L.mxq_host_workspace_bytes.restype = i64
         L.mxq_linear_fwd.argtypes = [vp, i32, i64, i64, i32, i32, f32, i32, i32, i32, vp, vp, i64, i32, vp, i32,
                                      i32, i32, vp, vp, i64, vp]
         L.mxq_linear_workspace_bytes.argtypes = [i64, i64]
@@ -147,6 +150,61 @@ def quantize_elemwise(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=Fal
                                           int(bits), int(exp_bits), float(max_norm), int(rmode),
                                           int(bool(saturate_normals)), int(bool(allow_denorm)),
                                           _ptr(noise), _stream(A)))
+    return out
+
+
+_host_ws = {}
+
+
+def _host_workspace(device):
+    ws = _host_ws.get(device.index)
+    if ws is None:
+        ws = torch.empty(lib().mxq_host_workspace_bytes(), dtype=torch.uint8, device=device)
+        _host_ws[device.index] = ws
+    return ws
+
+
+def quantize_mx_host(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False, rmode=0, out=None,
+                     device=None):
+    """MX-quantize a pinned HOST tensor on the GPU, result in pinned host memory (chunked, copies
+    overlapped with the kernel).  Returns after the result is complete."""
+    if A.is_cuda or not A.is_contiguous() or A.dtype not in _DT:
+        raise MxqError("quantize_mx_host needs a contiguous CPU tensor of a supported dtype")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if out is None:
+        out = torch.empty(A.shape, dtype=A.dtype, pin_memory=True)      # torch's caching host allocator
+    axis = axis % A.dim() if A.dim() else 0
+    pre, n, post = _split(list(A.shape), axis)
+    if A.numel():
+        with torch.cuda.device(device):
+            ws = _host_workspace(device)
+            st = torch.cuda.current_stream(device)
+            check(lib().mxq_quantize_mx_host(ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(out.data_ptr()), _DT[A.dtype],
+                                             pre, n, post, int(block) if block and block > 0 else n, int(scale_bits),
+                                             int(ebits), int(mbits), float(max_norm), int(bool(flush)), int(rmode),
+                                             _ptr(ws), ws.numel(), ctypes.c_void_p(st.cuda_stream)))
+            st.synchronize()
+    return out
+
+
+def quantize_elemwise_host(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=False, allow_denorm=True,
+                           out=None, out_dtype=None, device=None):
+    """Elementwise rounding of a pinned HOST tensor on the GPU; see quantize_mx_host."""
+    if A.is_cuda or not A.is_contiguous() or A.dtype not in _DT:
+        raise MxqError("quantize_elemwise_host needs a contiguous CPU tensor of a supported dtype")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if out is None:
+        out = torch.empty(A.shape, dtype=out_dtype or A.dtype, pin_memory=True)
+    if A.numel():
+        with torch.cuda.device(device):
+            ws = _host_workspace(device)
+            st = torch.cuda.current_stream(device)
+            check(lib().mxq_quantize_elemwise_host(ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                                   _DT[A.dtype], _DT[out.dtype], A.numel(), int(bits), int(exp_bits),
+                                                   float(max_norm), int(rmode), int(bool(saturate_normals)),
+                                                   int(bool(allow_denorm)), _ptr(ws), ws.numel(),
+                                                   ctypes.c_void_p(st.cuda_stream)))
+            st.synchronize()
     return out
 
 

@@ -75,6 +75,10 @@ def _quantize_elemwise_core(A, bits, exp_bits, max_norm, round="nearest", satura
         return _backend.quantize_elemwise(A.contiguous(), bits, exp_bits, max_norm, _MODE[round],
                                           saturate_normals, allow_denorm,
                                           noise.contiguous() if noise is not None else None)
+    if custom_cuda and round != "dither" and bits <= 24 and A.is_pinned() and A.is_contiguous() \
+            and torch.cuda.is_available():
+        from . import _backend
+        return _backend.quantize_elemwise_host(A, bits, exp_bits, max_norm, _MODE[round], saturate_normals, allow_denorm)
     return _round_host(A, bits, exp_bits, max_norm, round, saturate_normals, allow_denorm, noise)
 
 

@@ -103,6 +103,12 @@ def _quantize_mx(A, scale_bits, elem_format, shared_exp_method="max", axes=None,
                                     noise.contiguous() if noise is not None else None)
     if A.numel() == 0:
         return A.clone()
+    if custom_cuda and len(axes) == 1 and round != "dither" and A.is_pinned() and A.is_contiguous() \
+            and torch.cuda.is_available():
+        # a pinned host tensor with custom_cuda: quantize on the GPU, chunked, result back in pinned memory
+        from . import _backend
+        return _backend.quantize_mx_host(A, scale_bits, ebits, mbits, max_norm, block_size, axes[0],
+                                         flush_fp32_subnorms, _MODE[round])
     return _host_mx(A, scale_bits, ebits, mbits, max_norm, axes, block_size, round, flush_fp32_subnorms, noise)
 
 

@@ -250,3 +250,26 @@ def test_config2_full_size_properties(be):
     # elementwise bfloat16 round-even of an fp32 copy is the bf16 tensor itself
     y = be.quantize_elemwise(x.float(), 9, 8, 3.3895313892515355e38, 2, False, True, out_dtype=torch.bfloat16)
     assert torch.equal(y.view(torch.int16), x.view(torch.int16))
+
+
+@pytest.mark.parametrize("shape,axis", [((1024, 4096), 0), ((1024, 4096), 1), ((3, 700, 96), 1), ((5, 64, 33), 2),
+                                        ((40000,), 0), ((4100, 1000), 0)])
+def test_host_buffer_pipeline(be, shape, axis):
+    """mxq_quantize_mx_host / mxq_quantize_elemwise_host (chunked, copies overlapped) == device entry points,
+    also through quantize_mx_op on a pinned host tensor with custom_cuda."""
+    from microxcaling_b200.mx_ops import quantize_mx_op
+    from microxcaling_b200.specs import finalize_mx_specs
+    g = torch.Generator().manual_seed(12)
+    x = (torch.randn(shape, generator=g) * 3).to(torch.bfloat16)
+    hx = x.pin_memory()
+    eb, mb, mn = oracle.FORMATS["fp6_e2m3"]
+    want = be.quantize_mx(x.cuda(), 8, eb, mb, mn, 32, axis).cpu()
+    got = be.quantize_mx_host(hx, 8, eb, mb, mn, 32, axis)
+    assert not got.is_cuda and torch.equal(got.view(torch.int16), want.view(torch.int16))
+    sp = finalize_mx_specs({"a_elem_format": "fp6_e2m3", "block_size": 32, "custom_cuda": True})
+    got2 = quantize_mx_op(hx, sp, elem_format="fp6_e2m3", axes=[axis])
+    assert not got2.is_cuda and torch.equal(got2.view(torch.int16), want.view(torch.int16))
+    xf = x.float().pin_memory()
+    e_want = be.quantize_elemwise(xf.cuda(), 5, 8, 2.0 ** 127 * 1.875, 2).cpu()
+    e_got = be.quantize_elemwise_host(xf, 5, 8, 2.0 ** 127 * 1.875, 2)
+    assert torch.equal(e_got, e_want)
