@@ -26,6 +26,7 @@
 #include <cstring>
 #include "mxq_common.cuh"
 #include "sm100_ptx.cuh"
+#include "tma_host.cuh"
 
 namespace mxq {
 
@@ -348,22 +349,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // [batch, rows, K] bytes, K contiguous; box = 128 bytes of K x box_rows rows
 static int make_operand_map(CUtensorMap* m, const void* base, int64_t batch, int64_t rows, int64_t K, int box_rows) {
     EncodeTiledFn fn = encode_fn();

@@ -86,30 +86,31 @@ __device__ __forceinline__ float round_grid_abs(uint32_t a, const uint32_t emin_
     return fminf(r, max_norm);
 }
 
-// The same rounding applied directly to an unscaled magnitude ax = |x|: the
-// grid is the element format's grid multiplied by the block scale, so the
-// smallest-normal constant `cmin` = 2^(emin + s) * scale and the saturation
-// bound are per-block values and no multiply into or out of the scaled domain
-// is needed.  `smul` = 2^s with s = 23-P (half-away) or 24-P (other modes).
-// The rounding constant only has to lie in the right binade and be an even
-// multiple of the grid spacing; for sources with at most 11 significand bits
-// (bf16, fp16) ax * 2^s qualifies, which moves its computation from the
-// integer pipe to the FMA pipe.  Returns the rounded, unsaturated magnitude.
-// Valid when cmin and ax * 2^s are normal finite floats (the caller checks the
-// block's exponent range and otherwise uses the scaled-domain routine above).
-template <int MODE, bool NARROW_SRC>
-__device__ __forceinline__ float round_unscaled_abs(float ax, const float cmin, const float smul,
-                                                    const uint32_t k_field) {
-    float c;
-    if (MODE != RN_EVEN && NARROW_SRC)
-        c = fmaxf(ax * smul, cmin);
-    else
-        c = __uint_as_float(max((__float_as_uint(ax) & 0x7f800000u) + k_field, __float_as_uint(cmin)));
+// The same rounding applied directly to an unscaled magnitude ax = |x| of a
+// source with at most 11 significand bits (bf16, fp16): the grid is the element
+// format's grid multiplied by the block scale, so the smallest-normal constant
+// `cmin` = 2^(emin + s) * scale and the saturation bound are per-block values
+// and no multiply into or out of the scaled domain is needed.  `smul` = 2^s,
+// s = 24-P, so that the rounding constant c = max(ax * 2^s, cmin) has an ulp
+// equal to the grid spacing at ax.  c only has to lie in that binade and be an
+// even multiple of the spacing; with a narrow source ax * 2^s qualifies (its low
+// significand bits are zero and ax + c cannot leave the binade), which keeps the
+// computation on the FMA pipe.
+//   even:       RN(ax + c) - c
+//   floor:      RZ(ax + c) - c
+//   half-away:  RN(ax * (1 + 2^-12) + c) - c.  ax / spacing has at most 11
+//               significant bits, so the relative nudge is smaller than the
+//               distance of any non-tie from the next half-way point yet turns
+//               every exact tie into a round-up.
+// Returns the rounded, unsaturated magnitude.  Valid when cmin and ax * 2^s are
+// normal finite floats (the caller checks the block's exponent range and
+// otherwise uses the scaled-domain routine above).
+template <int MODE>
+__device__ __forceinline__ float round_unscaled_abs(float ax, const float cmin, const float smul) {
+    const float c = fmaxf(ax * smul, cmin);
     if (MODE == RN_EVEN) return __fadd_rn(ax, c) - c;
     if (MODE == RZ) return __fadd_rz(ax, c) - c;
-    uint32_t t = __float_as_uint(__fadd_rz(ax, c));
-    t = (t + 1u) & ~1u;
-    return __uint_as_float(t) - c;
+    return __fmaf_rn(ax, 1.000244140625f, c) - c;
 }
 
 // Biased exponent (0..255) of the block scale from the bits of the block's

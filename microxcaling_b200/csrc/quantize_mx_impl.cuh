@@ -130,10 +130,12 @@ __device__ __forceinline__ FastBlock fast_block(uint32_t amax_bits, const MxArgs
     const int E = scale_exp_from_absmax(amax_bits, a.fmt.emax_elem, a.scale_emax);
     const bool zero = amax_bits == 0;
     const int Ec = zero ? 127 : E;
-    const int field = (int)(a.fmt.emin_field >> 23) + (int)(a.fmt.k_field >> 23) + Ec - 127;
+    // rounding constants of the fast path sit at the full grid spacing (k_field is one less for half-away)
+    const uint32_t kf = a.fmt.k_field + (a.mode == RN_AWAY ? (1u << 23) : 0u);
+    const int field = (int)(a.fmt.emin_field >> 23) + (int)(kf >> 23) + Ec - 127;
     f.ok = zero || (Eraw >= 48 && Eraw <= 200 && E != 255 && field >= 1 && field < 254);
     f.E = E;
-    f.cmin = __uint_as_float(a.fmt.emin_field + a.fmt.k_field + ((uint32_t)(Ec - 127) << 23));
+    f.cmin = __uint_as_float(a.fmt.emin_field + kf + ((uint32_t)(Ec - 127) << 23));
     f.maxn = __uint_as_float(__float_as_uint(a.fmt.max_norm) + ((uint32_t)(Ec - 127) << 23));
     f.inv = inv_pow2_from_field(Ec);
     return f;
@@ -323,6 +325,12 @@ __device__ __forceinline__ uint32_t vmax_u16x2(uint32_t a, uint32_t b) {
     asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+// running maximum of two packed bf16 magnitudes: max(m, |w|) per lane, NaN-propagating
+__device__ __forceinline__ uint32_t amax_bf16x2(uint32_t m, uint32_t w) {
+    uint32_t r;
+    asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.NaN.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(m), "r"(w));
+    return r;
+}
 __device__ __forceinline__ uint32_t vmin_u16x2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -337,8 +345,10 @@ __device__ __forceinline__ uint32_t quant_pair_bf16(uint32_t w, float cmin_lo, f
                                                     float& r_lo, float& r_hi) {
     const float xl = __uint_as_float(w << 16);
     const float xh = __uint_as_float(w & 0xffff0000u);
-    r_lo = round_unscaled_abs<MODE, true>(fabsf(xl), cmin_lo, f.smul, f.k_field);
-    r_hi = round_unscaled_abs<MODE, true>(fabsf(xh), cmin_hi, f.smul, f.k_field);
+    // the fast path rounds at the full grid spacing in every mode (f.smul is half of that for half-away)
+    const float smul = MODE == RN_AWAY ? f.smul * 2.0f : f.smul;
+    r_lo = round_unscaled_abs<MODE>(fabsf(xl), cmin_lo, smul);
+    r_hi = round_unscaled_abs<MODE>(fabsf(xh), cmin_hi, smul);
     uint32_t p = __byte_perm(__float_as_uint(r_lo), __float_as_uint(r_hi), 0x7632);
     p = vmin_u16x2(p, maxn_pair);
     return p | (w & 0x80008000u);
@@ -398,8 +408,7 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
     for (int u = 0; u < kLastBfUnroll; ++u) {
         const int64_t v = base + (int64_t)u * kLastBfThreads + threadIdx.x;
         const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-        uint32_t m2 = vmax_u16x2(vmax_u16x2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu),
-                                 vmax_u16x2(w[2] & 0x7fff7fffu, w[3] & 0x7fff7fffu));
+        uint32_t m2 = amax_bf16x2(amax_bf16x2(amax_bf16x2(w[0] & 0x7fff7fffu, w[1]), w[2]), w[3]);
         uint32_t m = max(m2 & 0xffffu, m2 >> 16);
         for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
         const uint32_t amax = m << 16;
@@ -464,8 +473,8 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
         uint32_t m0 = 0, m1 = 0;
 #pragma unroll
         for (int r = 0; r < kMaxRows; ++r) {
-            m0 = vmax_u16x2(m0, raw[r].x & 0x7fff7fffu);
-            m1 = vmax_u16x2(m1, raw[r].y & 0x7fff7fffu);
+            m0 = amax_bf16x2(m0, raw[r].x);
+            m1 = amax_bf16x2(m1, raw[r].y);
         }
         const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
         FastBlock fb[4];

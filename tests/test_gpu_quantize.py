@@ -92,6 +92,38 @@ def test_mx_all_bf16_patterns(be, fmt, round):
                 want = oracle.quantize_mx(x, fmt, axis=axis, block=block, scale_bits=sb, round=round, flush=flush)
                 got = to_np(gpu_mx(be, x, fmt, axis, block, sb, round, flush))
                 assert oracle.same_values(got, want), (fmt, round, sb, axis, block, flush)
+                got = to_np(gpu_mx(be, torch.as_tensor(x).to(torch.bfloat16), fmt, axis, block, sb, round, flush))
+                assert oracle.same_values(got, want), (fmt, round, sb, axis, block, flush, "bf16 tensor")
+
+
+def _anchored_bf16_blocks():
+    """Blocks of 32 bf16 values: one anchor that fixes the block maximum, then 31
+    values from every (sign, mantissa) pattern at an exponent 0..17 binades below
+    it -- every tie and near-tie of the normal and subnormal range of each format."""
+    rows = []
+    for e0 in (60, 127, 190):
+        for anchor_m in (0x00, 0x7f):
+            anchor = (e0 << 7) | anchor_m
+            for k in range(0, 18):
+                pats = np.array([(s << 15) | ((e0 - k) << 7) | m for s in (0, 1) for m in range(128)], dtype=np.uint32)
+                pats = np.concatenate([pats, np.zeros((-len(pats)) % 31, dtype=np.uint32)]).reshape(-1, 31)
+                blk = np.concatenate([np.full((pats.shape[0], 1), anchor, dtype=np.uint32), pats], axis=1)
+                rows.append(blk)
+    return (np.concatenate(rows, axis=0) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("round", list(ROUNDS))
+def test_mx_bf16_ties_at_every_relative_exponent(be, fmt, round):
+    x = _anchored_bf16_blocks()                       # [n_blocks, 32]
+    want = oracle.quantize_mx(x, fmt, axis=-1, block=32, scale_bits=8, round=round)
+    n = x.shape[0] // 8 * 8
+    xt = np.ascontiguousarray(x[:n].T)                # blocks along axis 0, 8-aligned columns
+    for dt in (torch.bfloat16, torch.float32):        # the values are bf16 patterns: both casts are exact
+        got = to_np(gpu_mx(be, torch.as_tensor(x).to(dt), fmt, -1, 32, 8, round, False))
+        assert oracle.same_values(got, want), (fmt, round, dt, "last axis")
+        got = to_np(gpu_mx(be, torch.as_tensor(xt).to(dt), fmt, 0, 32, 8, round, False))
+        assert oracle.same_values(got, np.ascontiguousarray(want[:n].T)), (fmt, round, dt, "axis 0")
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
