@@ -369,10 +369,24 @@ __device__ __forceinline__ uint32_t code_pair(float q_lo, float q_hi, uint32_t w
 // Compact path for the blocks the fast path excludes: `rows` elements with
 // stride `stride` (in elements), re-read from global memory, scaled-domain
 // arithmetic, rolled loop (it runs rarely and must stay small).
-template <int MODE, int CK>
+// code-byte sinks of the slow path
+struct StridedBytes {                    // global memory, element r at p[r * s]
+    uint8_t* p;
+    int64_t s;
+    __device__ __forceinline__ void operator()(int r, uint8_t v) const { p[r * s] = v; }
+};
+struct StagedBytes {                     // one column of the transposed staging tile (see mx_strided_bf16_kernel)
+    uint8_t* tile;
+    int chunk0;                          // logical 16-byte chunk index of row 0
+    int swz;
+    __device__ __forceinline__ void operator()(int r, uint8_t v) const {
+        tile[(((chunk0 + (r >> 4)) ^ swz) << 4) + (r & 15)] = v;
+    }
+};
+
+template <int MODE, int CK, typename CodeSink>
 __device__ __forceinline__ void bf16_block_slow(const MxArgs& a, const uint16_t* in, int64_t first, int64_t stride,
-                                                int rows, uint32_t amax, uint8_t* codes_dst, int64_t codes_stride,
-                                                int pad_to) {
+                                                int rows, uint32_t amax, const CodeSink sink, int pad_to) {
     const BlockScale bs = block_scale(amax, a);
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
 #pragma unroll 1
@@ -380,11 +394,11 @@ __device__ __forceinline__ void bf16_block_slow(const MxArgs& a, const uint16_t*
         const uint32_t xb = (uint32_t)in[first + r * stride] << 16;
         const float q = quant_abs<MODE>(xb, bs, a.fmt);
         if (out) out[first + r * stride] = (uint16_t)((__float_as_uint(q * bs.scale) | (xb & 0x80000000u)) >> 16);
-        if (CK != CK_NONE) codes_dst[r * codes_stride] = (uint8_t)code_pair<CK>(q, 0.f, xb >> 16);
+        if (CK != CK_NONE) sink(r, (uint8_t)code_pair<CK>(q, 0.f, xb >> 16));
     }
     if (CK != CK_NONE) {
 #pragma unroll 1
-        for (int r = rows; r < pad_to; ++r) codes_dst[r * codes_stride] = 0;
+        for (int r = rows; r < pad_to; ++r) sink(r, 0);
     }
 }
 
@@ -418,7 +432,7 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
         if (!fb.ok) {
             if (live[u])
                 bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, amax,
-                                          CK != CK_NONE ? a.codes + v * 8 : nullptr, 1, 8);
+                                          StridedBytes{CK != CK_NONE ? a.codes + v * 8 : nullptr, 1}, 8);
             continue;
         }
         const uint32_t mp = (__float_as_uint(fb.maxn) >> 16) * 0x10001u;
@@ -441,20 +455,31 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
 
 constexpr int kStrBfThreads = 128;
 
-// TRANSPOSED (only with codes): codes and scales are written with the blocked axis innermost,
-// and a thread walks four consecutive blocks of its columns so that its stores to one output
-// row are 128 contiguous bytes and (in the GEMM scale layout) one 32-bit word of scales.
+// One thread owns 4 adjacent columns of one block (up to 32 rows).
+// TRANSPOSED (only with codes, block == 32): codes and scales are written with
+// the blocked axis innermost.  A thread walks four consecutive blocks of its
+// columns; the code bytes of two blocks at a time are staged in shared memory as
+// a [512 columns][64 bytes] tile and written out by the whole CTA, four lanes per
+// output row, so that a warp's store covers eight 64-byte segments instead of 32
+// scattered 16-byte ones.  The tile is addressed in 16-byte chunks,
+// chunk(c, j) = (4c + j) ^ ((c >> 2) & 7), which keeps both the per-column
+// writes and the row-major readout free of bank conflicts.  In the GEMM scale
+// layout the four scale bytes of a column are one 32-bit word.
 template <int MODE, bool WANT_DQ, int CK, bool TRANSPOSED>
-__global__ void __launch_bounds__(kStrBfThreads)
+__global__ void __launch_bounds__(kStrBfThreads, 4)
 mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nbgrp) {
     constexpr int kBlocksPerThread = TRANSPOSED ? 4 : 1;
+    __shared__ uint4 stage[TRANSPOSED ? kStrBfThreads * 4 * 4 : 1];
+    const int tid = threadIdx.x;
     const int64_t t = blockIdx.x;
     const int64_t ct = t % col_tiles;
     const int64_t pb = t / col_tiles;
     const int64_t bg = pb % nbgrp;
     const int64_t p = pb / nbgrp;
-    const int64_t col = ct * (kStrBfThreads * 4) + (int64_t)threadIdx.x * 4;
-    if (col >= a.post) return;
+    const int64_t col0 = ct * (kStrBfThreads * 4);
+    const int64_t col = col0 + (int64_t)tid * 4;
+    const bool active = col < a.post;
+    if (!TRANSPOSED && !active) return;
     const uint16_t* in = reinterpret_cast<const uint16_t*>(a.in);
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
     const int64_t padded = a.nblk * a.block;
@@ -462,96 +487,106 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
 #pragma unroll 1
     for (int bb = 0; bb < kBlocksPerThread; ++bb) {
         const int64_t b = bg * kBlocksPerThread + bb;
-        if (b >= a.nblk) break;
-        const int64_t row0 = b * a.block;
-        const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
-        const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
-        uint2 raw[kMaxRows];
+        if (b >= a.nblk) break;                                            // uniform over the CTA
+        if (active) {
+            const int64_t row0 = b * a.block;
+            const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
+            const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
+            uint2 raw[kMaxRows];
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r)
-            raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
-        uint32_t m0 = 0, m1 = 0;
+            for (int r = 0; r < kMaxRows; ++r)
+                raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
+            uint32_t m0 = 0, m1 = 0;
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r) {
-            m0 = amax_bf16x2(m0, raw[r].x);
-            m1 = amax_bf16x2(m1, raw[r].y);
-        }
-        const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
-        FastBlock fb[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
-        if (CK != CK_NONE) {
-            if (TRANSPOSED && a.sf_gemm) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) sf_word[i] |= (uint32_t)(fb[i].E & 0xff) << (8 * bb);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
+            for (int r = 0; r < kMaxRows; ++r) {
+                m0 = amax_bf16x2(m0, raw[r].x);
+                m1 = amax_bf16x2(m1, raw[r].y);
             }
-        }
-        if (!(fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok)) {
-#pragma unroll 1
-            for (int i = 0; i < 4; ++i) {
-                uint8_t* cd = nullptr;
-                int64_t cs = 0;
-                if (CK != CK_NONE) {
-                    if (TRANSPOSED) { cd = a.codes + (p * a.post + col + i) * padded + row0; cs = 1; }
-                    else { cd = a.codes + base + i; cs = a.post; }
-                }
-                const uint32_t mm = (i & 2) ? m1 : m0;
-                const uint32_t am = (i & 1) ? (mm & 0xffff0000u) : (mm << 16);
-                bf16_block_slow<MODE, CK>(a, in, base + i, a.post, rows, am, cd, cs, TRANSPOSED ? a.block : rows);
-            }
-            continue;
-        }
-        const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
-        const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
-        const float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
-        uint32_t tc[4][kMaxRows / 4];          // transposed codes: [column][4 rows per word]
+            const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
+            FastBlock fb[4];
 #pragma unroll
-        for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
-            uint32_t c01[4], c23[4];
+            for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
+            if (CK != CK_NONE) {
+                if (TRANSPOSED && a.sf_gemm) {
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) {
-                const int r = r4 * 4 + rr;
-                float q[4];
-                const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
-                const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
-                if (WANT_DQ && r < rows)
-                    *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
-                if (CK != CK_NONE) {
-                    c01[rr] = code_pair<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1], raw[r].x);
-                    c23[rr] = code_pair<CK>(fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].y);
-                    if (!TRANSPOSED && r < rows)
-                        *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01[rr] | (c23[rr] << 16);
-                }
-            }
-            if (CK != CK_NONE && TRANSPOSED) {
-                // 4 rows x 2 columns of code bytes -> one word per column (rows innermost)
-                const uint32_t t0 = __byte_perm(c01[0], c01[1], 0x5140), t1 = __byte_perm(c01[2], c01[3], 0x5140);
-                const uint32_t u0 = __byte_perm(c23[0], c23[1], 0x5140), u1 = __byte_perm(c23[2], c23[3], 0x5140);
-                tc[0][r4] = __byte_perm(t0, t1, 0x5410);
-                tc[1][r4] = __byte_perm(t0, t1, 0x7632);
-                tc[2][r4] = __byte_perm(u0, u1, 0x5410);
-                tc[3][r4] = __byte_perm(u0, u1, 0x7632);
-            }
-        }
-        if (CK != CK_NONE && TRANSPOSED) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint8_t* dst = a.codes + (p * a.post + col + i) * padded + row0;
-                if (a.block == kMaxRows) {
-                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
-                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(tc[i][4], tc[i][5], tc[i][6], tc[i][7]);
+                    for (int i = 0; i < 4; ++i) sf_word[i] |= (uint32_t)(fb[i].E & 0xff) << (8 * bb);
                 } else {
 #pragma unroll
-                    for (int r = 0; r < kMaxRows; ++r)
-                        if (r < a.block) dst[r] = (uint8_t)(tc[i][r >> 2] >> (8 * (r & 3)));
+                    for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
+                }
+            }
+            if (!(fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok)) {
+#pragma unroll 1
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t mm = (i & 2) ? m1 : m0;
+                    const uint32_t am = (i & 1) ? (mm & 0xffff0000u) : (mm << 16);
+                    if (TRANSPOSED)
+                        bf16_block_slow<MODE, CK>(a, in, base + i, a.post, rows, am,
+                                                  StagedBytes{reinterpret_cast<uint8_t*>(stage),
+                                                              (tid * 4 + i) * 4 + (bb & 1) * 2, tid & 7}, kMaxRows);
+                    else
+                        bf16_block_slow<MODE, CK>(a, in, base + i, a.post, rows, am,
+                                                  StridedBytes{CK != CK_NONE ? a.codes + base + i : nullptr, a.post}, rows);
+                }
+            } else {
+                const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
+                const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
+                const float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
+                uint32_t tc[4][4];                 // transposed codes: [column][4 rows per word], 16 rows
+#pragma unroll
+                for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
+                    uint32_t c01[4], c23[4];
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) {
+                        const int r = r4 * 4 + rr;
+                        float q[4];
+                        const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
+                        const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
+                        if (WANT_DQ && r < rows)
+                            *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
+                        if (CK != CK_NONE) {
+                            c01[rr] = code_pair<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1], raw[r].x);
+                            c23[rr] = code_pair<CK>(fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].y);
+                            if (!TRANSPOSED && r < rows)
+                                *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01[rr] | (c23[rr] << 16);
+                        }
+                    }
+                    if (CK != CK_NONE && TRANSPOSED) {
+                        // 4 rows x 2 columns of code bytes -> one word per column (rows innermost)
+                        const uint32_t t0 = __byte_perm(c01[0], c01[1], 0x5140), t1 = __byte_perm(c01[2], c01[3], 0x5140);
+                        const uint32_t u0 = __byte_perm(c23[0], c23[1], 0x5140), u1 = __byte_perm(c23[2], c23[3], 0x5140);
+                        tc[0][r4 & 3] = __byte_perm(t0, t1, 0x5410);
+                        tc[1][r4 & 3] = __byte_perm(t0, t1, 0x7632);
+                        tc[2][r4 & 3] = __byte_perm(u0, u1, 0x5410);
+                        tc[3][r4 & 3] = __byte_perm(u0, u1, 0x7632);
+                        if ((r4 & 3) == 3) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int chunk = (tid * 4 + i) * 4 + (bb & 1) * 2 + (r4 >> 2);
+                                stage[chunk ^ (tid & 7)] = make_uint4(tc[i][0], tc[i][1], tc[i][2], tc[i][3]);
+                            }
+                        }
+                    }
                 }
             }
         }
+        if (CK != CK_NONE && TRANSPOSED && ((bb & 1) || b + 1 >= a.nblk)) {
+            // write out the staged pair of blocks: 4 lanes per output row
+            __syncthreads();
+            const int nchunk = ((bb & 1) + 1) * 2;
+            const int64_t k0 = (bg * kBlocksPerThread + (bb & ~1)) * kMaxRows;
+#pragma unroll 4
+            for (int it = 0; it < 16; ++it) {
+                const int id = it * kStrBfThreads + tid;
+                const int c = id >> 2, j = id & 3;
+                if (col0 + c < a.post && j < nchunk)
+                    *reinterpret_cast<uint4*>(a.codes + (p * a.post + col0 + c) * padded + k0 + j * 16) =
+                        stage[id ^ ((id >> 4) & 7)];
+            }
+            __syncthreads();
+        }
     }
-    if (CK != CK_NONE && TRANSPOSED && a.sf_gemm) {
+    if (CK != CK_NONE && TRANSPOSED && a.sf_gemm && active) {
         const int64_t b0 = bg * kBlocksPerThread;
         const int nb = (int)min((int64_t)kBlocksPerThread, a.nblk - b0);
 #pragma unroll
@@ -700,7 +735,7 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
         }
     }
     if (fast_math && a.post > 1 && a.block <= kMaxRows && a.post % N8 == 0 && ptrs8) {
-        if (DT == DT_BF16 && P <= 8 && (!a.codes || (a.fmt.ebits != 0 && (!a.transposed || aligned16(a.codes)) && (!a.sf_gemm || !a.scales || (reinterpret_cast<uintptr_t>(a.scales) & 3u) == 0)))) {
+        if (DT == DT_BF16 && P <= 8 && (!a.codes || (a.fmt.ebits != 0 && (!a.transposed || (aligned16(a.codes) && a.block == kMaxRows)) && (!a.sf_gemm || !a.scales || (reinterpret_cast<uintptr_t>(a.scales) & 3u) == 0)))) {
             switch (a.mode) {
                 case RN_AWAY: return launch_strided_bf16<RN_AWAY>(a, st);
                 case RZ:      return launch_strided_bf16<RZ>(a, st);
