@@ -64,7 +64,29 @@ def check(status):
 
 
 def _stream(t):
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    """Raw handle of torch's current stream on t's device (an int; ctypes converts it)."""
+    idx = t.device.index
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device() if idx is None else idx)
+
+
+class _device_of:
+    """Makes t's device current around a library call; free when it already is."""
+    __slots__ = ("idx", "guard")
+
+    def __init__(self, dev):
+        idx = dev.index
+        self.idx = None if idx is None or idx == torch.cuda.current_device() else idx
+        self.guard = None
+
+    def __enter__(self):
+        if self.idx is not None:
+            self.guard = torch.cuda.device(self.idx)
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
 
 
 def _require_cuda(t, name="tensor"):
@@ -77,7 +99,7 @@ def _require_cuda(t, name="tensor"):
 
 
 def _ptr(t):
-    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else None
+    return t.data_ptr() if t is not None and t.numel() > 0 else None
 
 
 def _split(shape, axis):
@@ -110,22 +132,28 @@ def quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False,
     if want_codes:
         if transposed:
             codes = torch.empty(shape[:axis] + shape[axis + 1:] + [nblk * blk], dtype=torch.uint8, device=A.device)
-            scales = torch.empty(shape[:axis] + shape[axis + 1:] + [nblk], dtype=torch.uint8, device=A.device)
         else:
             codes = torch.empty(shape, dtype=torch.uint8, device=A.device)
-            scales = torch.empty(shape[:axis] + [nblk] + shape[axis + 1:], dtype=torch.uint8, device=A.device)
         if gemm_layout:
-            # [batch, rows, K] operand: 512-byte chunks per 128 rows x 128 K, padding defined as zero
+            # [batch, rows, K] operand: 512-byte chunks per 128 rows x 128 K; padding bytes are defined as
+            # zero (they exist only when rows or K is not a multiple of 128)
             if transposed:
                 nb, rows = pre, post
             else:
                 rows = rows_per_batch if rows_per_batch else pre
                 nb = pre // rows if rows else 0
-            scales = torch.zeros(lib().mxq_sf_bytes(nb, rows, nblk * blk), dtype=torch.uint8, device=A.device)
+            kpad = nblk * blk
+            nbytes = nb * ((rows + 127) // 128) * ((kpad + 127) // 128) * 512
+            alloc = torch.empty if rows % 128 == 0 and kpad % 128 == 0 else torch.zeros
+            scales = alloc(nbytes, dtype=torch.uint8, device=A.device)
+        elif transposed:
+            scales = torch.empty(shape[:axis] + shape[axis + 1:] + [nblk], dtype=torch.uint8, device=A.device)
+        else:
+            scales = torch.empty(shape[:axis] + [nblk] + shape[axis + 1:], dtype=torch.uint8, device=A.device)
     if noise is not None:
         _require_cuda(noise, "noise")
         assert noise.dtype == torch.float32 and noise.shape == A.shape
-    with torch.cuda.device(A.device):
+    with _device_of(A.device):
         check(lib().mxq_quantize_mx(_ptr(A), _ptr(out), _ptr(codes), _ptr(scales), _DT[A.dtype],
                                     pre, n, post, blk, int(scale_bits), int(ebits), int(mbits),
                                     float(max_norm), int(bool(flush)), int(rmode), _ptr(noise),
@@ -145,7 +173,7 @@ def quantize_elemwise(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=Fal
         raise MxqError("quantize_elemwise with bits > 24 leads to negative shifts")
     if noise is not None:
         _require_cuda(noise, "noise")
-    with torch.cuda.device(A.device):
+    with _device_of(A.device):
         check(lib().mxq_quantize_elemwise(_ptr(A), _ptr(out), _DT[A.dtype], _DT[out.dtype], A.numel(),
                                           int(bits), int(exp_bits), float(max_norm), int(rmode),
                                           int(bool(saturate_normals)), int(bool(allow_denorm)),
@@ -218,7 +246,7 @@ def gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, M, N, K, a_fmt=0, b_fmt
         out = torch.empty((batch, M, N), dtype=out_dtype, device=a_codes.device)
     if bias is not None:
         bias = bias.to(torch.float32).contiguous()
-    with torch.cuda.device(a_codes.device):
+    with _device_of(a_codes.device):
         check(lib().mxq_gemm_mx(_ptr(a_codes), _ptr(a_scales), _ptr(b_codes), _ptr(b_scales), _ptr(out),
                                 batch, M, N, K, a_fmt, b_fmt, _DT[out.dtype], int(bfloat_bits), int(round_mode),
                                 _ptr(bias), int(tile_n), _stream(a_codes)))
@@ -237,7 +265,7 @@ def linear_fwd(x, w_codes, w_scales, w_fmt, a_ebits, a_mbits, a_max_norm, a_roun
     y = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     if bias is not None:
         bias = bias.to(torch.float32).contiguous()
-    with torch.cuda.device(x.device):
+    with _device_of(x.device):
         check(lib().mxq_linear_fwd(_ptr(x), _DT[x.dtype], M, K, int(a_ebits), int(a_mbits), float(a_max_norm),
                                    int(a_round), int(scale_bits), int(bool(flush)), _ptr(w_codes), _ptr(w_scales),
                                    N, int(w_fmt), _ptr(y), _DT[y.dtype], int(bfloat_bits), int(out_round),
@@ -257,7 +285,7 @@ def _reduce(A, fn):
     inner = A.shape[-1]
     rows = A.numel() // inner if inner else 0
     out = torch.empty(A.shape[:-1], dtype=A.dtype, device=A.device)
-    with torch.cuda.device(A.device):
+    with _device_of(A.device):
         check(fn(_ptr(A), _ptr(out), rows, inner, _stream(A)))
     return out
 

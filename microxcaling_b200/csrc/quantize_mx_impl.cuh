@@ -59,7 +59,35 @@ struct MxArgs {
     FastDiv div_nblk;       // last-axis kernels: block index -> (row, block in row)
     FastDiv div_rpb;        // row -> (batch, row in batch)
     ElemFmt fmt;
+    // unscaled fast path of the bf16 kernels (set_fast_consts)
+    uint32_t fp_e_lo, fp_e_span;   // usable iff (exponent field of the block maximum - fp_e_lo) <= fp_e_span
+    uint32_t fp_cmin_base;         // bits of cmin   = fp_cmin_base + (E << 23)
+    uint32_t fp_maxn_base;         // bits of maxn   = fp_maxn_base + (E << 23)
+    uint32_t fp_mp_base;           // packed bf16 maxn pair = fp_mp_base + E * 0x00800080
 };
+
+// The unscaled fast path needs its per-block constants to be normal, finite
+// floats and the scale exponent to need no clamping; both hold when the block
+// maximum's exponent field lies in one launch-constant interval, computed here.
+__host__ inline void set_fast_consts(MxArgs& a) {
+    const int emin_f = (int)(a.fmt.emin_field >> 23);
+    // rounding constants sit at the full grid spacing in every mode (k_field is one less for half-away)
+    const int kf_f = (int)(a.fmt.k_field >> 23) + (a.mode == RN_AWAY ? 1 : 0);
+    const int ee = a.fmt.emax_elem;
+    int lo = 48, hi = 200;
+    lo = std::max(lo, 127 - a.scale_emax + ee);          // scale exponent not clamped
+    hi = std::min(hi, 127 + a.scale_emax + ee);
+    lo = std::max(lo, 1 - emin_f - kf_f + 127 + ee);      // cmin normal and finite
+    hi = std::min(hi, 253 - emin_f - kf_f + 127 + ee);
+    uint32_t mn;
+    memcpy(&mn, &a.fmt.max_norm, 4);
+    const int mp_half = (int)(mn >> 16) - (127 << 7);
+    if (lo > hi || mp_half < 0 || (mn & 0xffffu) != 0) { a.fp_e_lo = 0xffffff00u; a.fp_e_span = 0; }
+    else { a.fp_e_lo = (uint32_t)lo; a.fp_e_span = (uint32_t)(hi - lo); }
+    a.fp_cmin_base = ((uint32_t)(emin_f + kf_f) << 23) - (127u << 23);
+    a.fp_maxn_base = mn - (127u << 23);
+    a.fp_mp_base = (uint32_t)(mp_half < 0 ? 0 : mp_half) * 0x10001u;
+}
 
 // Last-axis kernels: byte index of the scale of linear block index `blk`
 // (row-major over [rows, nblk]); 32-bit arithmetic with invariant divisors.
@@ -111,33 +139,26 @@ __device__ __forceinline__ float quant_abs(uint32_t xb, const BlockScale& s, con
     return round_grid_abs<MODE>(__float_as_uint(v), f.emin_field, f.k_field, f.max_norm);
 }
 
-// Per-block constants of the unscaled fast path (see round_unscaled_abs).
-// The fast path needs the rounding constants to be normal, finite floats, which
-// holds when the block maximum lies in a wide middle range of exponents; other
-// blocks (tiny or huge maxima, NaN/Inf, flushed) are marked !ok and go through a
-// compact scaled-domain loop instead.
+// Per-block constants of the unscaled fast path (see round_unscaled_abs), from
+// the exponent field (0..255) of the block maximum.  Blocks outside the usable
+// interval (tiny or huge maxima, zero, NaN/Inf, flushed) are marked !ok and go
+// through a compact scaled-domain loop instead; their E is not meaningful.
 struct FastBlock {
     float cmin;      // 2^(emin + s) * scale
     float maxn;      // max_norm * scale
     float inv;       // 1 / scale, for the element codes
-    int E;           // biased scale exponent (E8M0 byte)
+    uint32_t E;      // biased scale exponent (E8M0 byte)
     bool ok;
 };
 
-__device__ __forceinline__ FastBlock fast_block(uint32_t amax_bits, const MxArgs& a) {
+__device__ __forceinline__ FastBlock fast_block(uint32_t eraw, const MxArgs& a) {
     FastBlock f;
-    const int Eraw = (int)(amax_bits >> 23);
-    const int E = scale_exp_from_absmax(amax_bits, a.fmt.emax_elem, a.scale_emax);
-    const bool zero = amax_bits == 0;
-    const int Ec = zero ? 127 : E;
-    // rounding constants of the fast path sit at the full grid spacing (k_field is one less for half-away)
-    const uint32_t kf = a.fmt.k_field + (a.mode == RN_AWAY ? (1u << 23) : 0u);
-    const int field = (int)(a.fmt.emin_field >> 23) + (int)(kf >> 23) + Ec - 127;
-    f.ok = zero || (Eraw >= 48 && Eraw <= 200 && E != 255 && field >= 1 && field < 254);
-    f.E = E;
-    f.cmin = __uint_as_float(a.fmt.emin_field + kf + ((uint32_t)(Ec - 127) << 23));
-    f.maxn = __uint_as_float(__float_as_uint(a.fmt.max_norm) + ((uint32_t)(Ec - 127) << 23));
-    f.inv = inv_pow2_from_field(Ec);
+    f.ok = (eraw - a.fp_e_lo) <= a.fp_e_span;
+    f.E = eraw - (uint32_t)a.fmt.emax_elem;
+    const uint32_t e23 = f.E << 23;
+    f.cmin = __uint_as_float(a.fp_cmin_base + e23);
+    f.maxn = __uint_as_float(a.fp_maxn_base + e23);
+    f.inv = __uint_as_float((254u << 23) - e23);
     return f;
 }
 
@@ -331,6 +352,12 @@ __device__ __forceinline__ uint32_t amax_bf16x2(uint32_t m, uint32_t w) {
     asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.NaN.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(m), "r"(w));
     return r;
 }
+// min(m, |w|) per packed bf16 lane (m, w not NaN)
+__device__ __forceinline__ uint32_t amin_bf16x2(uint32_t m, uint32_t w) {
+    uint32_t r;
+    asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmin.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(m), "r"(w));
+    return r;
+}
 __device__ __forceinline__ uint32_t vmin_u16x2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -339,16 +366,26 @@ __device__ __forceinline__ uint32_t vmin_u16x2(uint32_t a, uint32_t b) {
 
 // two bf16 elements (word w) -> two dequantized bf16 elements, fast path.
 // lo/hi constants may differ (strided kernel: adjacent columns).
-template <int MODE>
+// PRE_CLAMP: saturation is applied to the packed magnitudes before rounding
+// (max_norm * scale is a grid point and rounding is monotonic, so this equals
+// saturating afterwards) and r_lo / r_hi return saturated magnitudes; otherwise
+// the packed result is saturated and r_lo / r_hi are not.  The first form is
+// cheaper but keeps a second copy of the inputs alive, which only the kernels
+// with few registers in flight can afford.
+template <int MODE, bool PRE_CLAMP>
 __device__ __forceinline__ uint32_t quant_pair_bf16(uint32_t w, float cmin_lo, float cmin_hi,
                                                     uint32_t maxn_pair, const ElemFmt& f,
                                                     float& r_lo, float& r_hi) {
-    const float xl = __uint_as_float(w << 16);
-    const float xh = __uint_as_float(w & 0xffff0000u);
     // the fast path rounds at the full grid spacing in every mode (f.smul is half of that for half-away)
     const float smul = MODE == RN_AWAY ? f.smul * 2.0f : f.smul;
-    r_lo = round_unscaled_abs<MODE>(fabsf(xl), cmin_lo, smul);
-    r_hi = round_unscaled_abs<MODE>(fabsf(xh), cmin_hi, smul);
+    if (PRE_CLAMP) {
+        const uint32_t ax = amin_bf16x2(maxn_pair, w);
+        r_lo = round_unscaled_abs<MODE>(__uint_as_float(ax << 16), cmin_lo, smul);
+        r_hi = round_unscaled_abs<MODE>(__uint_as_float(ax & 0xffff0000u), cmin_hi, smul);
+        return __byte_perm(__float_as_uint(r_lo), __float_as_uint(r_hi), 0x7632) | (w & 0x80008000u);
+    }
+    r_lo = round_unscaled_abs<MODE>(fabsf(__uint_as_float(w << 16)), cmin_lo, smul);
+    r_hi = round_unscaled_abs<MODE>(fabsf(__uint_as_float(w & 0xffff0000u)), cmin_hi, smul);
     uint32_t p = __byte_perm(__float_as_uint(r_lo), __float_as_uint(r_hi), 0x7632);
     p = vmin_u16x2(p, maxn_pair);
     return p | (w & 0x80008000u);
@@ -365,10 +402,15 @@ __device__ __forceinline__ uint32_t code_pair(float q_lo, float q_hi, uint32_t w
     const float sh = __uint_as_float(__float_as_uint(q_hi) | (w & 0x80000000u));
     return CK == CK_E5M2 ? encode2_e5m2(sl, sh) : encode2_e4m3(sl, sh);
 }
+// four scaled magnitudes + the signs of the two source pairs -> four code bytes:
+// the sign bits are moved into place for all four bytes at once
+template <int CK>
+__device__ __forceinline__ uint32_t code_quad(float q0, float q1, float q2, float q3, uint32_t w01, uint32_t w23) {
+    const uint32_t lo = CK == CK_E5M2 ? encode2_e5m2(q0, q1) : encode2_e4m3(q0, q1);
+    const uint32_t hi = CK == CK_E5M2 ? encode2_e5m2(q2, q3) : encode2_e4m3(q2, q3);
+    return __byte_perm(lo, hi, 0x5410) | (__byte_perm(w01, w23, 0x7531) & 0x80808080u);
+}
 
-// Compact path for the blocks the fast path excludes: `rows` elements with
-// stride `stride` (in elements), re-read from global memory, scaled-domain
-// arithmetic, rolled loop (it runs rarely and must stay small).
 // code-byte sinks of the slow path
 struct StridedBytes {                    // global memory, element r at p[r * s]
     uint8_t* p;
@@ -389,6 +431,19 @@ __device__ __forceinline__ void bf16_block_slow(const MxArgs& a, const uint16_t*
                                                 int rows, uint32_t amax, const CodeSink sink, int pad_to) {
     const BlockScale bs = block_scale(amax, a);
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+    if (amax == 0) {                       // a block of (signed) zeros passes through
+#pragma unroll 1
+        for (int r = 0; r < rows; ++r) {
+            const uint16_t x = in[first + r * stride];
+            if (out) out[first + r * stride] = x;
+            if (CK != CK_NONE) sink(r, (uint8_t)((x >> 8) & 0x80u));
+        }
+        if (CK != CK_NONE) {
+#pragma unroll 1
+            for (int r = rows; r < pad_to; ++r) sink(r, 0);
+        }
+        return;
+    }
 #pragma unroll 1
     for (int r = 0; r < rows; ++r) {
         const uint32_t xb = (uint32_t)in[first + r * stride] << 16;
@@ -405,49 +460,58 @@ __device__ __forceinline__ void bf16_block_slow(const MxArgs& a, const uint16_t*
 constexpr int kLastBfThreads = 256;
 constexpr int kLastBfUnroll = 4;
 
+// A warp owns 2 KB of consecutive input (4 x 32 lanes x 16 bytes); a block of 32
+// elements is shared by `lanes_per_block` neighbouring lanes.  `row_local`: every
+// warp's 32 blocks lie in one row of the GEMM scale layout (4 lanes per block and
+// a multiple of 32 blocks per row), so the scale index is computed once per thread.
 template <int MODE, bool WANT_DQ, int CK>
 __global__ void __launch_bounds__(kLastBfThreads)
-mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block) {
+mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block, const int row_local) {
     const int lane_shift = 31 - __clz(lanes_per_block);
-    const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll);
+    const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll) +
+                         (threadIdx.x >> 5) * (32 * kLastBfUnroll) + (threadIdx.x & 31);
     uint4 raw[kLastBfUnroll];
     bool live[kLastBfUnroll];
 #pragma unroll
     for (int u = 0; u < kLastBfUnroll; ++u) {
-        const int64_t v = base + (int64_t)u * kLastBfThreads + threadIdx.x;
+        const int64_t v = base + u * 32;
         live[u] = v < nvec;
         raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in) + v) : make_uint4(0, 0, 0, 0);
     }
+    int64_t sidx0 = 0;
+    if (CK != CK_NONE && row_local) sidx0 = scale_index_last(a, (uint32_t)(base >> 2));
 #pragma unroll
     for (int u = 0; u < kLastBfUnroll; ++u) {
-        const int64_t v = base + (int64_t)u * kLastBfThreads + threadIdx.x;
+        const int64_t v = base + u * 32;
         const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
         uint32_t m2 = amax_bf16x2(amax_bf16x2(amax_bf16x2(w[0] & 0x7fff7fffu, w[1]), w[2]), w[3]);
         uint32_t m = max(m2 & 0xffffu, m2 >> 16);
         for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
-        const uint32_t amax = m << 16;
-        const FastBlock fb = fast_block(amax, a);
-        if (CK != CK_NONE && live[u] && (threadIdx.x & (lanes_per_block - 1)) == 0)
-            a.scales[scale_index_last(a, (uint32_t)(v >> lane_shift))] = (uint8_t)fb.E;
+        const FastBlock fb = fast_block(m >> 7, a);
+        if (CK != CK_NONE && live[u] && (threadIdx.x & (lanes_per_block - 1)) == 0) {
+            // 8 blocks further along the row = two 512-byte chunks of the GEMM scale layout
+            const int64_t sidx = row_local ? sidx0 + u * 1024 : scale_index_last(a, (uint32_t)(v >> lane_shift));
+            a.scales[sidx] = (uint8_t)(fb.ok ? fb.E : (uint32_t)scale_exp_from_absmax(m << 16, a.fmt.emax_elem, a.scale_emax));
+        }
         if (!fb.ok) {
             if (live[u])
-                bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, amax,
+                bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, m << 16,
                                           StridedBytes{CK != CK_NONE ? a.codes + v * 8 : nullptr, 1}, 8);
             continue;
         }
-        const uint32_t mp = (__float_as_uint(fb.maxn) >> 16) * 0x10001u;
+        const uint32_t mp = a.fp_mp_base + fb.E * 0x00800080u;
         uint32_t o[4];
         float q[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = quant_pair_bf16<MODE>(w[i], fb.cmin, fb.cmin, mp, a.fmt, q[2 * i], q[2 * i + 1]);
+        for (int i = 0; i < 4; ++i) o[i] = quant_pair_bf16<MODE, true>(w[i], fb.cmin, fb.cmin, mp, a.fmt, q[2 * i], q[2 * i + 1]);
         if (!live[u]) continue;
         if (WANT_DQ) reinterpret_cast<uint4*>(a.out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
         if (CK != CK_NONE) {
             uint32_t c[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-                c[i] = code_pair<CK>(fminf(q[4 * i], fb.maxn) * fb.inv, fminf(q[4 * i + 1], fb.maxn) * fb.inv, w[2 * i]) |
-                       (code_pair<CK>(fminf(q[4 * i + 2], fb.maxn) * fb.inv, fminf(q[4 * i + 3], fb.maxn) * fb.inv, w[2 * i + 1]) << 16);
+                c[i] = code_quad<CK>(q[4 * i] * fb.inv, q[4 * i + 1] * fb.inv, q[4 * i + 2] * fb.inv, q[4 * i + 3] * fb.inv,
+                                     w[2 * i], w[2 * i + 1]);
             reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
         }
     }
@@ -502,20 +566,27 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
                 m0 = amax_bf16x2(m0, raw[r].x);
                 m1 = amax_bf16x2(m1, raw[r].y);
             }
-            const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
+            const uint32_t eraw[4] = {(m0 >> 7) & 0xffu, m0 >> 23, (m1 >> 7) & 0xffu, m1 >> 23};
             FastBlock fb[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) fb[i] = fast_block(amax[i], a);
+            for (int i = 0; i < 4; ++i) fb[i] = fast_block(eraw[i], a);
+            const bool all_ok = fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
             if (CK != CK_NONE) {
+                uint32_t E[4] = {fb[0].E, fb[1].E, fb[2].E, fb[3].E};
+                if (!all_ok) {
+                    const uint32_t amax[4] = {m0 << 16, m0 & 0xffff0000u, m1 << 16, m1 & 0xffff0000u};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) E[i] = (uint32_t)scale_exp_from_absmax(amax[i], a.fmt.emax_elem, a.scale_emax);
+                }
                 if (TRANSPOSED && a.sf_gemm) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) sf_word[i] |= (uint32_t)(fb[i].E & 0xff) << (8 * bb);
+                    for (int i = 0; i < 4; ++i) sf_word[i] |= (E[i] & 0xffu) << (8 * bb);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)fb[i].E;
+                    for (int i = 0; i < 4; ++i) a.scales[scale_index(a, p, b, col + i)] = (uint8_t)E[i];
                 }
             }
-            if (!(fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok)) {
+            if (!all_ok) {
 #pragma unroll 1
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t mm = (i & 2) ? m1 : m0;
@@ -529,32 +600,32 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
                                                   StridedBytes{CK != CK_NONE ? a.codes + base + i : nullptr, a.post}, rows);
                 }
             } else {
-                const uint32_t mp0 = (__float_as_uint(fb[0].maxn) >> 16) | (__float_as_uint(fb[1].maxn) & 0xffff0000u);
-                const uint32_t mp1 = (__float_as_uint(fb[2].maxn) >> 16) | (__float_as_uint(fb[3].maxn) & 0xffff0000u);
+                const uint32_t mp0 = a.fp_mp_base + ((fb[0].E | (fb[1].E << 16)) << 7);
+                const uint32_t mp1 = a.fp_mp_base + ((fb[2].E | (fb[3].E << 16)) << 7);
                 const float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
                 uint32_t tc[4][4];                 // transposed codes: [column][4 rows per word], 16 rows
 #pragma unroll
                 for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
-                    uint32_t c01[4], c23[4];
+                    uint32_t c4[4];
 #pragma unroll
                     for (int rr = 0; rr < 4; ++rr) {
                         const int r = r4 * 4 + rr;
                         float q[4];
-                        const uint32_t o0 = quant_pair_bf16<MODE>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
-                        const uint32_t o1 = quant_pair_bf16<MODE>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
+                        const uint32_t o0 = quant_pair_bf16<MODE, false>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
+                        const uint32_t o1 = quant_pair_bf16<MODE, false>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
                         if (WANT_DQ && r < rows)
                             *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
                         if (CK != CK_NONE) {
-                            c01[rr] = code_pair<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1], raw[r].x);
-                            c23[rr] = code_pair<CK>(fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].y);
+                            c4[rr] = code_quad<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1],
+                                                   fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].x, raw[r].y);
                             if (!TRANSPOSED && r < rows)
-                                *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c01[rr] | (c23[rr] << 16);
+                                *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c4[rr];
                         }
                     }
                     if (CK != CK_NONE && TRANSPOSED) {
-                        // 4 rows x 2 columns of code bytes -> one word per column (rows innermost)
-                        const uint32_t t0 = __byte_perm(c01[0], c01[1], 0x5140), t1 = __byte_perm(c01[2], c01[3], 0x5140);
-                        const uint32_t u0 = __byte_perm(c23[0], c23[1], 0x5140), u1 = __byte_perm(c23[2], c23[3], 0x5140);
+                        // 4 rows x 4 columns of code bytes -> one word per column (rows innermost)
+                        const uint32_t t0 = __byte_perm(c4[0], c4[1], 0x5140), t1 = __byte_perm(c4[2], c4[3], 0x5140);
+                        const uint32_t u0 = __byte_perm(c4[0], c4[1], 0x7362), u1 = __byte_perm(c4[2], c4[3], 0x7362);
                         tc[0][r4 & 3] = __byte_perm(t0, t1, 0x5410);
                         tc[1][r4 & 3] = __byte_perm(t0, t1, 0x7632);
                         tc[2][r4 & 3] = __byte_perm(u0, u1, 0x5410);
@@ -672,11 +743,12 @@ static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream
     if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
     const unsigned g = (unsigned)grid;
     const bool e5 = a.fmt.ebits == 5;
-    if (!a.codes) mx_lastaxis_bf16_kernel<MODE, true, CK_NONE><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else if (a.out && e5) mx_lastaxis_bf16_kernel<MODE, true, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else if (a.out) mx_lastaxis_bf16_kernel<MODE, true, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else if (e5) mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
-    else mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes);
+    const int rl = a.sf_gemm && lanes == 4 && a.nblk % 32 == 0;
+    if (!a.codes) mx_lastaxis_bf16_kernel<MODE, true, CK_NONE><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
+    else if (a.out && e5) mx_lastaxis_bf16_kernel<MODE, true, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
+    else if (a.out) mx_lastaxis_bf16_kernel<MODE, true, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
+    else if (e5) mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
+    else mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
     return check_launch();
 }
 
