@@ -136,6 +136,29 @@ int mxq_reduce_sum_inner(const void* in, void* out, int64_t rows, int64_t inner,
 int mxq_reduce_max_inner(const void* in, void* out, int64_t rows, int64_t inner, void* stream);
 
 /*
+ * Fused bfloat16 vector chains.  The reference runs these layers as one
+ * elementwise kernel per vector operation, each followed by a rounding to the
+ * bfloat format (mx/vector_ops.py:1-130); for bfloat16 CUDA tensors with
+ * bfloat = 16 every step computes in fp32 and rounds to nearest-even bfloat16.
+ * These entry points run the same chain per element in registers.
+ *
+ * mxq_silu_bf16: SiLUFunction.forward (mx/activations.py:418-439)
+ *   e = exp(-g); a = e + 1; sig = 1 / a; out = g * sig; with `up`: out = out * up
+ *   (the simd_mul of a gated feed-forward block, mx/simd_ops.py:189-237).
+ *   gate, up, out, sig: n bfloat16 elements, 16-byte aligned; up and sig may be NULL.
+ * mxq_rmsnorm_bf16: RMSNormFunction.forward (mx/layernorm.py:113-129)
+ *   ms = mean(x*x); rinv = 1/sqrt(ms + eps); x_norm = x * rinv; out = weight * x_norm + bias
+ *   over the last dimension of x [rows, hidden]; the row sum is accumulated in
+ *   fp32 and rounded to bfloat16 once (like the library reduction the reference
+ *   calls, whose summation order is unspecified).  bias, x_norm [rows, hidden]
+ *   and rms_inv [rows] may be NULL.  hidden % 8 == 0 needs 16-byte aligned
+ *   pointers; other widths take an element-wise path.
+ */
+int mxq_silu_bf16(const void* gate, const void* up, void* out, void* sig, int64_t n, void* stream);
+int mxq_rmsnorm_bf16(const void* x, const void* weight, const void* bias, void* out, void* x_norm,
+                     void* rms_inv, int64_t rows, int64_t hidden, float eps, void* stream);
+
+/*
  * Block-scaled MX GEMM on the tensor cores (tcgen05 kind::mxf8f6f4):
  *   C[b] = A[b] (M x K) * B[b]^T (N x K),  b < batch, fp32 accumulation.
  * Takes the place of the library GEMM the reference runs on dequantized

@@ -54,6 +54,8 @@ def lib():
         L.mxq_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, vp]
         L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
+        L.mxq_silu_bf16.argtypes = [vp, vp, vp, vp, i64, vp]
+        L.mxq_rmsnorm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
         _lib = L
     return _lib
 
@@ -271,6 +273,43 @@ def linear_fwd(x, w_codes, w_scales, w_fmt, a_ebits, a_mbits, a_max_norm, a_roun
                                    N, int(w_fmt), _ptr(y), _DT[y.dtype], int(bfloat_bits), int(out_round),
                                    _ptr(bias), _ptr(workspace), workspace.numel(), _stream(x)))
     return y, workspace
+
+
+def _require_bf16(t, name):
+    if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.bfloat16):
+        raise MxqError("%s must be a contiguous bfloat16 CUDA tensor" % name)
+
+
+def silu_bf16(gate, up=None, want_sig=False):
+    """Fused bfloat16 SiLU chain (times `up` if given); see mxq_silu_bf16.  Returns out or (out, sig)."""
+    _require_bf16(gate, "gate")
+    if up is not None:
+        _require_bf16(up, "up")
+        if up.shape != gate.shape:
+            raise MxqError("gate and up must have the same shape")
+    out = torch.empty_like(gate)
+    sig = torch.empty_like(gate) if want_sig else None
+    with _device_of(gate.device):
+        check(lib().mxq_silu_bf16(_ptr(gate), _ptr(up), _ptr(out), _ptr(sig), gate.numel(), _stream(gate)))
+    return (out, sig) if want_sig else out
+
+
+def rmsnorm_bf16(x, weight, bias, eps, want_saved=False):
+    """Fused bfloat16 RMSNorm over the last dimension; see mxq_rmsnorm_bf16.
+    Returns out or (out, x_norm, rms_inv)."""
+    _require_bf16(x, "x")
+    _require_bf16(weight, "weight")
+    if bias is not None:
+        _require_bf16(bias, "bias")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    out = torch.empty_like(x)
+    xn = torch.empty_like(x) if want_saved else None
+    ri = torch.empty(x.shape[:-1] + (1,), dtype=x.dtype, device=x.device) if want_saved else None
+    with _device_of(x.device):
+        check(lib().mxq_rmsnorm_bf16(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(xn), _ptr(ri), rows, hidden,
+                                     float(eps), _stream(x)))
+    return (out, xn, ri) if want_saved else out
 
 
 def device_status(clear=True):

@@ -5,7 +5,7 @@ import torch
 import torch.nn.functional as F
 
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
-from .vector_ops import vec_add, vec_exp, vec_mul, vec_quantize, vec_recip, vec_sub
+from .vector_ops import fused_bf16_ok, vec_add, vec_exp, vec_mul, vec_quantize, vec_recip, vec_sub
 
 f_silu = F.silu
 
@@ -16,9 +16,13 @@ class SiLUFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, inplace=False, mx_specs=None, name=None):
         sp = mx_specs
-        q_in = vec_quantize(input, mx_specs=sp)
-        sig = vec_recip(vec_add(vec_exp(-q_in, mx_specs=sp), 1.0, mx_specs=sp), mx_specs=sp)
-        out = vec_mul(q_in, sig, mx_specs=sp)
+        if fused_bf16_ok(sp, input):
+            from . import _backend
+            out, sig = _backend.silu_bf16(input.contiguous(), None, want_sig=True)
+        else:
+            q_in = vec_quantize(input, mx_specs=sp)
+            sig = vec_recip(vec_add(vec_exp(-q_in, mx_specs=sp), 1.0, mx_specs=sp), mx_specs=sp)
+            out = vec_mul(q_in, sig, mx_specs=sp)
         if inplace:
             ctx.mark_dirty(input)
             input.copy_(out)

@@ -1,0 +1,198 @@
+// Fused bfloat16 vector chains (sm_100a): SiLU (optionally times a second
+// tensor) and RMSNorm.
+//
+// The reference builds these layers from single vector operations, each
+// followed by a rounding to the bfloat format (mx/vector_ops.py:1-130,
+// mx/activations.py:418-455, mx/layernorm.py:98-200); on bfloat16 CUDA tensors
+// with bfloat = 16 every such step is one elementwise kernel over the whole
+// tensor that computes in fp32 and rounds the result to bfloat16
+// (round-to-nearest-even).  The kernels here run the same chain of fp32
+// operations and bfloat16 roundings per element in registers, so a layer reads
+// its inputs once and writes its outputs once: HBM-bound streaming kernels,
+// 16-byte accesses, grid sized from the SM count.
+#include "mxq_common.cuh"
+#include <cuda_bf16.h>
+#include <algorithm>
+
+namespace mxq {
+
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// fp32 -> nearest-even bfloat16, as a float
+__device__ __forceinline__ float rb(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ uint32_t pack_bf(float lo, float hi) {
+    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);   // both already on the bf16 grid
+}
+
+// sigmoid and SiLU of one bfloat16 value q with every intermediate rounded to
+// bfloat16: e = exp(-q), a = e + 1, s = 1 / a, y = q * s  (mx/activations.py:428-434)
+__device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
+    const float e = rb(expf(-q));
+    const float a = rb(e + 1.0f);
+    s = rb(1.0f / a);
+    y = rb(q * s);
+}
+
+constexpr int kVecThreads = 256;
+
+template <bool HAS_UP, bool WANT_SIG>
+__global__ void __launch_bounds__(kVecThreads)
+silu_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
+                 uint4* __restrict__ sig, const int64_t nvec, const int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * kVecThreads;
+    for (int64_t v = (int64_t)blockIdx.x * kVecThreads + threadIdx.x; v < nvec; v += stride) {
+        const uint4 g4 = __ldg(gate + v);
+        uint4 u4 = make_uint4(0, 0, 0, 0);
+        if (HAS_UP) u4 = __ldg(up + v);
+        const uint32_t g[4] = {g4.x, g4.y, g4.z, g4.w};
+        const uint32_t u[4] = {u4.x, u4.y, u4.z, u4.w};
+        uint32_t o[4], sg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float s0, y0, s1, y1;
+            silu_chain(bf_lo(g[i]), s0, y0);
+            silu_chain(bf_hi(g[i]), s1, y1);
+            if (HAS_UP) { y0 = rb(y0 * bf_lo(u[i])); y1 = rb(y1 * bf_hi(u[i])); }
+            o[i] = pack_bf(y0, y1);
+            sg[i] = pack_bf(s0, s1);
+        }
+        out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (WANT_SIG) sig[v] = make_uint4(sg[0], sg[1], sg[2], sg[3]);
+    }
+    // ragged tail (n not a multiple of 8): one thread per element
+    const int64_t t = nvec * 8 + (int64_t)blockIdx.x * kVecThreads + threadIdx.x;
+    if (t < n) {
+        const uint16_t* g = reinterpret_cast<const uint16_t*>(gate);
+        float s, y;
+        silu_chain(__uint_as_float((uint32_t)g[t] << 16), s, y);
+        if (HAS_UP) y = rb(y * __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(up)[t] << 16));
+        reinterpret_cast<uint16_t*>(out)[t] = (uint16_t)(__float_as_uint(y) >> 16);
+        if (WANT_SIG) reinterpret_cast<uint16_t*>(sig)[t] = (uint16_t)(__float_as_uint(s) >> 16);
+    }
+}
+
+// RMSNorm of one row per CTA (mx/layernorm.py:113-125):
+//   ms = mean(x*x), r = 1/sqrt(ms + eps), xn = x * r, y = w * xn + b
+// with a bfloat16 rounding after every operation; the row sum is accumulated in
+// fp32 and rounded once, like a library reduction.  The row is read twice, the
+// second time from cache.
+constexpr int kNormThreads = 256;
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
+                    uint16_t* __restrict__ out, uint16_t* __restrict__ xnorm, uint16_t* __restrict__ rinv,
+                    const int64_t rows, const int64_t hidden, const float inv_hidden, const float eps) {
+    __shared__ float part[kNormThreads / 32];
+    __shared__ float r_shared;
+    const bool vec = (hidden & 7) == 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint16_t* xr = x + row * hidden;
+        float acc = 0.f;
+        if (vec) {
+            const uint4* xv = reinterpret_cast<const uint4*>(xr);
+            for (int64_t i = threadIdx.x; i < hidden / 8; i += kNormThreads) {
+                const uint4 v = __ldg(xv + i);
+                const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float lo = bf_lo(q[k]), hi = bf_hi(q[k]);
+                    acc += rb(lo * lo);
+                    acc += rb(hi * hi);
+                }
+            }
+        } else {
+            for (int64_t i = threadIdx.x; i < hidden; i += kNormThreads) {
+                const float v = __uint_as_float((uint32_t)xr[i] << 16);
+                acc += rb(v * v);
+            }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.f;
+#pragma unroll
+            for (int k = 0; k < kNormThreads / 32; ++k) tot += part[k];
+            const float sum = rb(tot);
+            const float ms = rb(sum * inv_hidden);           // division by a host scalar = multiply by its reciprocal
+            const float t = rb(ms + eps);
+            const float r = rb(sqrtf(t));
+            const float ri = rb(1.0f / r);
+            r_shared = ri;
+            if (rinv) rinv[row] = (uint16_t)(__float_as_uint(ri) >> 16);
+        }
+        __syncthreads();
+        const float ri = r_shared;
+        uint16_t* orow = out + row * hidden;
+        uint16_t* nrow = xnorm ? xnorm + row * hidden : nullptr;
+        if (vec) {
+            const uint4* xv = reinterpret_cast<const uint4*>(xr);
+            const uint4* wv = reinterpret_cast<const uint4*>(w);
+            const uint4* bv = reinterpret_cast<const uint4*>(b);
+            for (int64_t i = threadIdx.x; i < hidden / 8; i += kNormThreads) {
+                const uint4 v = __ldg(xv + i), ww = __ldg(wv + i);
+                uint4 bb = make_uint4(0, 0, 0, 0);
+                if (b) bb = __ldg(bv + i);
+                const uint32_t q[4] = {v.x, v.y, v.z, v.w}, wq[4] = {ww.x, ww.y, ww.z, ww.w}, bq[4] = {bb.x, bb.y, bb.z, bb.w};
+                uint32_t o[4], nn[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float n0 = rb(bf_lo(q[k]) * ri), n1 = rb(bf_hi(q[k]) * ri);
+                    float y0 = rb(bf_lo(wq[k]) * n0), y1 = rb(bf_hi(wq[k]) * n1);
+                    if (b) { y0 = rb(y0 + bf_lo(bq[k])); y1 = rb(y1 + bf_hi(bq[k])); }
+                    o[k] = pack_bf(y0, y1);
+                    nn[k] = pack_bf(n0, n1);
+                }
+                reinterpret_cast<uint4*>(orow)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                if (nrow) reinterpret_cast<uint4*>(nrow)[i] = make_uint4(nn[0], nn[1], nn[2], nn[3]);
+            }
+        } else {
+            for (int64_t i = threadIdx.x; i < hidden; i += kNormThreads) {
+                const float n0 = rb(__uint_as_float((uint32_t)xr[i] << 16) * ri);
+                float y0 = rb(__uint_as_float((uint32_t)w[i] << 16) * n0);
+                if (b) y0 = rb(y0 + __uint_as_float((uint32_t)b[i] << 16));
+                orow[i] = (uint16_t)(__float_as_uint(y0) >> 16);
+                if (nrow) nrow[i] = (uint16_t)(__float_as_uint(n0) >> 16);
+            }
+        }
+        __syncthreads();                                      // part / r_shared are reused by the next row
+    }
+}
+
+}  // namespace mxq
+
+extern "C" int mxq_silu_bf16(const void* gate, const void* up, void* out, void* sig, int64_t n, void* stream) {
+    using namespace mxq;
+    if (n < 0) return MXQ_ERR_BAD_ARG;
+    if (n == 0) return MXQ_OK;
+    if (!gate || !out) return MXQ_ERR_BAD_ARG;
+    if (!aligned16(gate) || !aligned16(out) || (up && !aligned16(up)) || (sig && !aligned16(sig))) return MXQ_ERR_BAD_ARG;
+    const int64_t nvec = n / 8;
+    const int64_t want = std::max<int64_t>((nvec + kVecThreads - 1) / kVecThreads, ((n - nvec * 8) + kVecThreads - 1) / kVecThreads);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sm_count() * 16));
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint4 *g = (const uint4*)gate, *u = (const uint4*)up;
+    uint4 *o = (uint4*)out, *s = (uint4*)sig;
+    if (up && sig) silu_bf16_kernel<true, true><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
+    else if (up) silu_bf16_kernel<true, false><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
+    else if (sig) silu_bf16_kernel<false, true><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
+    else silu_bf16_kernel<false, false><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
+    return check_launch();
+}
+
+extern "C" int mxq_rmsnorm_bf16(const void* x, const void* weight, const void* bias, void* out, void* x_norm,
+                                void* rms_inv, int64_t rows, int64_t hidden, float eps, void* stream) {
+    using namespace mxq;
+    if (rows < 0 || hidden < 0) return MXQ_ERR_BAD_ARG;
+    if (rows == 0 || hidden == 0) return MXQ_OK;
+    if (!x || !weight || !out) return MXQ_ERR_BAD_ARG;
+    if ((hidden & 7) == 0 && (!aligned16(x) || !aligned16(weight) || !aligned16(out) || (bias && !aligned16(bias)) ||
+                              (x_norm && !aligned16(x_norm))))
+        return MXQ_ERR_BAD_ARG;
+    const unsigned grid = (unsigned)std::min<int64_t>(rows, (int64_t)sm_count() * 8);
+    rmsnorm_bf16_kernel<<<grid, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const uint16_t*)x, (const uint16_t*)weight, (const uint16_t*)bias, (uint16_t*)out, (uint16_t*)x_norm,
+        (uint16_t*)rms_inv, rows, hidden, 1.0f / (float)hidden, eps);
+    return check_launch();
+}

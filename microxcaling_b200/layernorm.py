@@ -3,7 +3,7 @@ itself is outside the scope of this package."""
 import torch
 
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
-from .vector_ops import (vec_add, vec_mul, vec_quantize, vec_recip, vec_reduce_mean, vec_reduce_sum,
+from .vector_ops import (fused_bf16_ok, vec_add, vec_mul, vec_quantize, vec_recip, vec_reduce_mean, vec_reduce_sum,
                          vec_sqrt, vec_sub)
 
 
@@ -11,13 +11,19 @@ class RMSNormFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps, mx_specs=None, name=None):
         sp = mx_specs
-        x = vec_quantize(x, mx_specs=sp)
-        ms = vec_reduce_mean(vec_mul(x, x, mx_specs=sp), -1, keepdim=True, mx_specs=sp)
-        rms_inv = vec_recip(vec_sqrt(vec_add(ms, eps, mx_specs=sp), mx_specs=sp), mx_specs=sp)
-        x_norm = vec_mul(x, rms_inv, mx_specs=sp)
-        bf_w = vec_quantize(weight, mx_specs=sp)
-        bf_b = vec_quantize(bias, mx_specs=sp)
-        out = vec_add(vec_mul(bf_w, x_norm, mx_specs=sp), bf_b, mx_specs=sp)
+        if fused_bf16_ok(sp, x, weight, bias) and x.shape[-1] == weight.numel() == bias.numel():
+            from . import _backend
+            out, x_norm, rms_inv = _backend.rmsnorm_bf16(x.contiguous(), weight.contiguous(), bias.contiguous(), eps,
+                                                         want_saved=True)
+            bf_w = weight
+        else:
+            x = vec_quantize(x, mx_specs=sp)
+            ms = vec_reduce_mean(vec_mul(x, x, mx_specs=sp), -1, keepdim=True, mx_specs=sp)
+            rms_inv = vec_recip(vec_sqrt(vec_add(ms, eps, mx_specs=sp), mx_specs=sp), mx_specs=sp)
+            x_norm = vec_mul(x, rms_inv, mx_specs=sp)
+            bf_w = vec_quantize(weight, mx_specs=sp)
+            bf_b = vec_quantize(bias, mx_specs=sp)
+            out = vec_add(vec_mul(bf_w, x_norm, mx_specs=sp), bf_b, mx_specs=sp)
         ctx.save_for_backward(x_norm, rms_inv, bf_w if sp["quantize_backprop"] else weight)
         ctx.mx_specs = get_backwards_mx_specs(sp)
         return out

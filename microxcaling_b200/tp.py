@@ -28,6 +28,7 @@ from ._mxgemm import _MODE, _fast_ok, _fmt, _pack, mx_gemm
 from .elemwise_ops import quantize_elemwise_op
 from .formats import _get_format_params
 from .specs import apply_mx_specs
+from .vector_ops import fused_bf16_ok
 
 
 def shard_bounds(n, rank, world, multiple=1):
@@ -128,7 +129,10 @@ class TensorParallelFFN(torch.nn.Module):
                           round_mode=out_rnd)[0]
         up = be.gemm_mx(xc, xs, uc, us, 1, T, Il, self.hidden, xk, uk, out_dtype=h.dtype, bfloat_bits=bits,
                         round_mode=out_rnd)[0]
-        act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
+        if fused_bf16_ok(sp, gate, up):
+            act = be.silu_bf16(gate, up)                      # SiLU(gate) * up, one pass
+        else:
+            act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
         act = quantize_elemwise_op(act, sp, round=sp["round_output"])
         ac, as_, ak = _pack(act, af, sp, rnd, True)
         if self.world == 1:

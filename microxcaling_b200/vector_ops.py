@@ -15,6 +15,19 @@ def _q(x, mx_specs, round):
     return quantize_elemwise_op(x, mx_specs=mx_specs, round=round)
 
 
+def fused_bf16_ok(mx_specs, *tensors):
+    """True when a chain of vector ops on these tensors is 'fp32 op, round to
+    nearest-even bfloat16' at every step, i.e. bfloat16 CUDA tensors whose
+    vector format (bfloatX, X >= 16) leaves bfloat16 values untouched; such
+    chains have fused kernels in libmxq (mxq_silu_bf16, mxq_rmsnorm_bf16)."""
+    sp = mx_specs
+    if not sp or sp["fp"] > 0 or sp["bfloat"] < 16 or not sp["bfloat_subnorms"]:
+        return False
+    if sp["round"] not in ("nearest", "floor", "even") or sp["vec_use_exp2"] or sp["vec_use_recip"]:
+        return False
+    return all(t is not None and t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+
+
 def vec_quantize(input, mx_specs=None, round=None):
     return _q(input, mx_specs, round)
 
