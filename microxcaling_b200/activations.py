@@ -18,7 +18,10 @@ class SiLUFunction(torch.autograd.Function):
         sp = mx_specs
         if fused_bf16_ok(sp, input):
             from . import _backend
-            out, sig = _backend.silu_bf16(input.contiguous(), None, want_sig=True)
+            if ctx.needs_input_grad[0]:
+                out, sig = _backend.silu_bf16(input.contiguous(), None, want_sig=True)
+            else:
+                out, sig = _backend.silu_bf16(input.contiguous(), None), None
         else:
             q_in = vec_quantize(input, mx_specs=sp)
             sig = vec_recip(vec_add(vec_exp(-q_in, mx_specs=sp), 1.0, mx_specs=sp), mx_specs=sp)
@@ -27,7 +30,8 @@ class SiLUFunction(torch.autograd.Function):
             ctx.mark_dirty(input)
             input.copy_(out)
             out = input
-        ctx.save_for_backward(out, sig)
+        if sig is not None:
+            ctx.save_for_backward(out, sig)
         ctx.mx_specs = get_backwards_mx_specs(sp)
         return out
 

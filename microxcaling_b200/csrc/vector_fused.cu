@@ -29,7 +29,7 @@ __device__ __forceinline__ uint32_t pack_bf(float lo, float hi) {
 __device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
     const float e = rb(expf(-q));
     const float a = rb(e + 1.0f);
-    s = rb(1.0f / a);
+    s = rb(__frcp_rn(a));                 // correctly rounded, hence equal to 1.0f / a
     y = rb(q * s);
 }
 
@@ -118,7 +118,7 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
             const float ms = rb(sum * inv_hidden);           // division by a host scalar = multiply by its reciprocal
             const float t = rb(ms + eps);
             const float r = rb(sqrtf(t));
-            const float ri = rb(1.0f / r);
+            const float ri = rb(__frcp_rn(r));               // = 1.0f / r (both correctly rounded)
             r_shared = ri;
             if (rinv) rinv[row] = (uint16_t)(__float_as_uint(ri) >> 16);
         }

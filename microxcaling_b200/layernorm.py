@@ -13,8 +13,13 @@ class RMSNormFunction(torch.autograd.Function):
         sp = mx_specs
         if fused_bf16_ok(sp, x, weight, bias) and x.shape[-1] == weight.numel() == bias.numel():
             from . import _backend
-            out, x_norm, rms_inv = _backend.rmsnorm_bf16(x.contiguous(), weight.contiguous(), bias.contiguous(), eps,
-                                                         want_saved=True)
+            if any(ctx.needs_input_grad[:3]):
+                out, x_norm, rms_inv = _backend.rmsnorm_bf16(x.contiguous(), weight.contiguous(), bias.contiguous(),
+                                                             eps, want_saved=True)
+            else:                                             # inference: nothing is kept for backward
+                out = _backend.rmsnorm_bf16(x.contiguous(), weight.contiguous(), bias.contiguous(), eps)
+                ctx.mx_specs = get_backwards_mx_specs(sp)
+                return out
             bf_w = weight
         else:
             x = vec_quantize(x, mx_specs=sp)
