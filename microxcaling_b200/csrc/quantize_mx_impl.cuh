@@ -530,7 +530,7 @@ constexpr int kStrBfThreads = 128;
 // writes and the row-major readout free of bank conflicts.  In the GEMM scale
 // layout the four scale bytes of a column are one 32-bit word.
 template <int MODE, bool WANT_DQ, int CK, bool TRANSPOSED>
-__global__ void __launch_bounds__(kStrBfThreads, 4)
+__global__ void __launch_bounds__(kStrBfThreads, (CK == CK_NONE && !TRANSPOSED) ? 6 : 4)
 mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nbgrp) {
     constexpr int kBlocksPerThread = TRANSPOSED ? 4 : 1;
     __shared__ uint4 stage[TRANSPOSED ? kStrBfThreads * 4 * 4 : 1];
