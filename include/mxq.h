@@ -188,6 +188,26 @@ int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void* b_codes, 
 int64_t mxq_sf_bytes(int64_t batch, int64_t rows, int64_t K);
 
 /*
+ * Scattering GEMM for a row-parallel layer split over several GPUs (no
+ * reference counterpart: the reference is single-device).  Same product as
+ * mxq_gemm_mx with batch = 1 and no bias, but rows
+ * [d * rows_per_dest, (d+1) * rows_per_dest) of the result are stored into
+ * dests[d], a [rows_per_dest, N] buffer that may live on another GPU (a peer
+ * mapping in this process).  Each 128-row tile leaves through a bulk store as
+ * soon as it is finished, so the transfer overlaps the remaining tiles; nothing
+ * waits on another GPU inside the kernel.  The caller orders the consumers
+ * (a barrier between ranks after the call), then adds the slabs it received
+ * with mxq_sum_slabs_f32.  rows_per_dest % 128 == 0, n_dests <= 8,
+ * N * element size % 16 == 0, M <= n_dests * rows_per_dest.
+ */
+int mxq_gemm_mx_scatter(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                        void* const* dests, int n_dests, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K,
+                        int a_fmt, int b_fmt, int out_dtype, int out_bfloat_bits, int out_round, int tile_n,
+                        void* stream);
+/* out[i] = ((slab0[i] + slab1[i]) + slab2[i]) + ...  for n_slabs consecutive fp32 slabs of elems_per_slab. */
+int mxq_sum_slabs_f32(const void* slabs, int n_slabs, int64_t elems_per_slab, void* out, void* stream);
+
+/*
  * Forward of an MX linear layer whose weights were packed once:
  *   y[M,N] = round(MX(x)[M,K] * W[N,K]^T (+ bias)),
  * i.e. the activation quantization (mx/linear.py:62-68, block 32 along K) and

@@ -55,6 +55,9 @@ def lib():
         L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_silu_bf16.argtypes = [vp, vp, vp, vp, i64, vp]
+        L.mxq_gemm_mx_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i32, i32, i32,
+                                          i32, i32, i32, vp]
+        L.mxq_sum_slabs_f32.argtypes = [vp, i32, i64, vp, vp]
         L.mxq_rmsnorm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
         _lib = L
     return _lib
@@ -252,6 +255,30 @@ def gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, M, N, K, a_fmt=0, b_fmt
         check(lib().mxq_gemm_mx(_ptr(a_codes), _ptr(a_scales), _ptr(b_codes), _ptr(b_scales), _ptr(out),
                                 batch, M, N, K, a_fmt, b_fmt, _DT[out.dtype], int(bfloat_bits), int(round_mode),
                                 _ptr(bias), int(tile_n), _stream(a_codes)))
+    return out
+
+
+def gemm_mx_scatter(a_codes, a_scales, b_codes, b_scales, dest_ptrs, rows_per_dest, M, N, K, a_fmt=0, b_fmt=0,
+                    out_dtype=torch.float32, bfloat_bits=0, round_mode=-1, tile_n=0):
+    """A @ B^T with rows [d*rows_per_dest, (d+1)*rows_per_dest) stored into the buffer at dest_ptrs[d]
+    (device pointers, possibly peer mappings); see mxq_gemm_mx_scatter."""
+    for t in (a_codes, b_codes, a_scales, b_scales):
+        if not t.is_cuda or not t.is_contiguous() or t.dtype != torch.uint8:
+            raise MxqError("GEMM operands must be contiguous uint8 CUDA tensors")
+    arr = (ctypes.c_void_p * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
+    with _device_of(a_codes.device):
+        check(lib().mxq_gemm_mx_scatter(_ptr(a_codes), _ptr(a_scales), _ptr(b_codes), _ptr(b_scales), arr,
+                                        len(dest_ptrs), int(rows_per_dest), M, N, K, a_fmt, b_fmt, _DT[out_dtype],
+                                        int(bfloat_bits), int(round_mode), int(tile_n), _stream(a_codes)))
+
+
+def sum_slabs(slabs):
+    """slabs [n, ...] fp32 -> their sum over dim 0, added in order; see mxq_sum_slabs_f32."""
+    if not (slabs.is_cuda and slabs.is_contiguous() and slabs.dtype == torch.float32):
+        raise MxqError("slabs must be a contiguous float32 CUDA tensor")
+    out = torch.empty(slabs.shape[1:], dtype=torch.float32, device=slabs.device)
+    with _device_of(slabs.device):
+        check(lib().mxq_sum_slabs_f32(_ptr(slabs), slabs.shape[0], out.numel(), _ptr(out), _stream(slabs)))
     return out
 
 

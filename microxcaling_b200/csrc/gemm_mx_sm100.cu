@@ -76,6 +76,17 @@ struct GemmArgs {
     int epi_kind;               // 0/1/2: bf16 out, bfloat16 rounding nearest/floor/even, no bias; 3: generic
     int bf16_exact;             // rounded values are bf16 values: pack upper halves
     int c_tma;                  // output written by TMA stores (row pitch multiple of 16 bytes)
+    int64_t rows_per_dest;      // > 0: output rows [d * rows_per_dest, (d+1) * rows_per_dest) go to destination d
+};
+
+// Output tensor maps.  A plain GEMM uses m[0].  The scattering GEMM of a
+// row-parallel layer has one map per destination buffer (its own memory or a
+// peer GPU's, mapped into this process): every 128-row tile of the result is
+// stored straight into the buffer of the rank that owns those rows, tile by
+// tile while the other tiles are still being computed.
+constexpr int kMaxDests = 8;
+struct OutMaps {
+    CUtensorMap m[kMaxDests];
 };
 
 template <int BN, int STAGES>
@@ -110,7 +121,7 @@ __device__ __forceinline__ void tile_coords(int64_t t, const GemmArgs& g, int64_
 template <int BN, int STAGES, int ACC_BUFS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
+               const __grid_constant__ OutMaps tmaps_c, const GemmArgs g) {
     using S = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -250,6 +261,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ptx::tc_fence_after();
             if (warp == 2 && lane == 0) TRACE(600 + 2 * tile_i);
             const int64_t row0 = mt * kBM + q * 32;
+            // destination of this tile's rows (128-row tiles never straddle destinations)
+            const int64_t dest = g.rows_per_dest > 0 ? row0 / g.rows_per_dest : 0;
+            const int64_t row0_dest = row0 - dest * g.rows_per_dest;
+            const CUtensorMap* tmap_c = &tmaps_c.m[dest];
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN;
             // Read this warp's whole share of the accumulator (BN/2 columns) into registers first
             // and hand the tensor-memory buffer back to the MMA warp at once; rounding and stores
@@ -314,7 +329,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         ptx::fence_proxy_async();
                         __syncwarp();
                         if (lane == 0) {
-                            ptx::tma_store_3d(&tmap_c, stg, (int)col0, (int)row0, (int)bi);
+                            ptx::tma_store_3d(tmap_c, stg, (int)col0, (int)row0_dest, (int)bi);
                             ptx::bulk_commit();
                         }
                     } else if (row0 + lane < g.M) {
@@ -391,7 +406,7 @@ static int make_output_map(CUtensorMap* m, void* base, int64_t batch, int64_t M,
 }
 
 template <int BN, int STAGES, int ACC_BUFS>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g,
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, const GemmArgs& g,
                        cudaStream_t st) {
     using S = GemmSmem<BN, STAGES>;
     auto kern = gemm_mx_kernel<BN, STAGES, ACC_BUFS>;
@@ -416,7 +431,15 @@ namespace mxq {
 int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
                         void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
                         int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
-                        int* status_word, void* stream) {
+                        int* status_word, void* stream, void* const* dests, int n_dests, int64_t rows_per_dest) {
+    if (n_dests > 0) {
+        if (!dests || n_dests > kMaxDests || rows_per_dest <= 0 || rows_per_dest % kBM != 0 || batch != 1 ||
+            M > n_dests * rows_per_dest)
+            return MXQ_ERR_BAD_ARG;
+        for (int d = 0; d < n_dests; ++d)
+            if (!dests[d] || !aligned16(dests[d])) return MXQ_ERR_BAD_ARG;
+        c = dests[0];
+    }
     if (batch < 0 || M < 0 || N < 0 || K < 0) return MXQ_ERR_BAD_ARG;
     if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
     if (!a_codes || !a_scales || !b_codes || !b_scales || !c) return MXQ_ERR_BAD_ARG;
@@ -455,14 +478,22 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     if (rc) return rc;
     rc = make_operand_map(&tb, b_codes, batch, N, K, bn);
     if (rc) return rc;
-    CUtensorMap tc;
+    OutMaps tc;
     const int64_t es = out_dtype == MXQ_F32 ? 4 : 2;
     g.c_tma = (N * es) % 16 == 0;
-    if (g.c_tma) {
-        rc = make_output_map(&tc, c, batch, M, N, out_dtype == MXQ_F32);
+    g.rows_per_dest = n_dests > 0 ? rows_per_dest : 0;
+    for (int d = 0; d < kMaxDests; ++d) tc.m[d] = ta;                  // placeholders, never dereferenced
+    if (n_dests > 0) {
+        if (!g.c_tma) return MXQ_ERR_UNSUPPORTED;                      // destinations are written by TMA stores only
+        for (int d = 0; d < n_dests; ++d) {
+            const int64_t rows = std::min<int64_t>(rows_per_dest, M - d * rows_per_dest);   // the last one may be ragged
+            if (rows <= 0) break;
+            rc = make_output_map(&tc.m[d], dests[d], 1, rows, N, out_dtype == MXQ_F32);
+            if (rc) return rc;
+        }
+    } else if (g.c_tma) {
+        rc = make_output_map(&tc.m[0], c, batch, M, N, out_dtype == MXQ_F32);
         if (rc) return rc;
-    } else {
-        tc = ta;                                   // unused by the kernel
     }
     if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
     return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
@@ -478,7 +509,20 @@ extern "C" int mxq_gemm_mx(const void* a_codes, const void* a_scales, const void
     int* word = mxq::device_status_word();
     if (!word) return MXQ_ERR_CUDA;
     return mxq::gemm_mx_with_status(a_codes, a_scales, b_codes, b_scales, c, batch, M, N, K, a_fmt, b_fmt, out_dtype,
-                                    out_bfloat_bits, out_round, bias, tile_n, word, stream);
+                                    out_bfloat_bits, out_round, bias, tile_n, word, stream, nullptr, 0, 0);
+}
+
+extern "C" int mxq_gemm_mx_scatter(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                                   void* const* dests, int n_dests, int64_t rows_per_dest, int64_t M, int64_t N,
+                                   int64_t K, int a_fmt, int b_fmt, int out_dtype, int out_bfloat_bits, int out_round,
+                                   int tile_n, void* stream) {
+    if (M < 0 || N < 0 || K < 0 || n_dests <= 0) return MXQ_ERR_BAD_ARG;
+    if (M == 0 || N == 0) return MXQ_OK;
+    int* word = mxq::device_status_word();
+    if (!word) return MXQ_ERR_CUDA;
+    return mxq::gemm_mx_with_status(a_codes, a_scales, b_codes, b_scales, nullptr, 1, M, N, K, a_fmt, b_fmt, out_dtype,
+                                    out_bfloat_bits, out_round, nullptr, tile_n, word, stream, dests, n_dests,
+                                    rows_per_dest);
 }
 
 extern "C" int mxq_device_status(int clear) {

@@ -12,7 +12,8 @@ namespace mxq {
 int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
                         void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int a_fmt, int b_fmt,
                         int out_dtype, int out_bfloat_bits, int out_round, const void* bias, int tile_n,
-                        int* status_word, void* stream);
+                        int* status_word, void* stream, void* const* dests = nullptr, int n_dests = 0,
+                        int64_t rows_per_dest = 0);
 
 static inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 

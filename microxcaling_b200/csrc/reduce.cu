@@ -106,3 +106,35 @@ extern "C" int mxq_reduce_sum_inner(const void* in, void* out, int64_t rows, int
 extern "C" int mxq_reduce_max_inner(const void* in, void* out, int64_t rows, int64_t inner, void* stream) {
     return mxq::reduce_inner<true>(in, out, rows, inner, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Sum of n fp32 slabs of equal size, added in slab order (the reduction step
+// after a scattering GEMM: slab s holds the partial sums rank s produced).
+// ---------------------------------------------------------------------------
+namespace mxq {
+constexpr int kSumThreads = 256;
+__global__ void __launch_bounds__(kSumThreads)
+sum_slabs_kernel(const float4* __restrict__ slabs, float4* __restrict__ out, const int n_slabs, const int64_t vec_per_slab) {
+    const int64_t stride = (int64_t)gridDim.x * kSumThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kSumThreads + threadIdx.x; i < vec_per_slab; i += stride) {
+        float4 acc = __ldg(slabs + i);
+        for (int s = 1; s < n_slabs; ++s) {
+            const float4 v = __ldg(slabs + (int64_t)s * vec_per_slab + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        out[i] = acc;
+    }
+}
+}  // namespace mxq
+
+extern "C" int mxq_sum_slabs_f32(const void* slabs, int n_slabs, int64_t elems_per_slab, void* out, void* stream) {
+    using namespace mxq;
+    if (n_slabs <= 0 || elems_per_slab < 0) return MXQ_ERR_BAD_ARG;
+    if (elems_per_slab == 0) return MXQ_OK;
+    if (!slabs || !out) return MXQ_ERR_BAD_ARG;
+    if (elems_per_slab % 4 != 0 || !aligned16(slabs) || !aligned16(out)) return MXQ_ERR_ALIGN;
+    const int64_t nvec = elems_per_slab / 4;
+    const unsigned grid = (unsigned)std::min<int64_t>((nvec + kSumThreads - 1) / kSumThreads, (int64_t)sm_count() * 16);
+    sum_slabs_kernel<<<grid, kSumThreads, 0, (cudaStream_t)stream>>>((const float4*)slabs, (float4*)out, n_slabs, nvec);
+    return check_launch();
+}

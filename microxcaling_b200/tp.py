@@ -15,11 +15,19 @@ its FFN admits without changing results beyond fp32 accumulation order:
   * down is row-parallel: each rank contracts over its slice of `intermediate`
     (a multiple of 32, so MX blocks never straddle ranks), the fp32 partial sums
     are reduce-scattered over tokens and rounded to bfloat once, after the sum.
+    On GPUs with peer access the scatter is part of the GEMM: every finished
+    128-row tile is stored straight into the receive buffer of the rank that
+    owns those tokens (mxq_gemm_mx_scatter), one small NCCL all-reduce orders
+    the ranks, and each rank adds the slabs it received in rank order
+    (mxq_sum_slabs_f32).  MXQ_TP_FUSED_SCATTER=0 selects the NCCL
+    reduce-scatter instead.
 
 On CUDA tensors the GEMMs run on packed operands through libmxq; on CPU tensors
 (used by the gloo tests of this logic) the same steps run on fake-quantized
 values with torch's GEMM.  `world_size == 1` skips the collectives.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -40,6 +48,31 @@ def shard_bounds(n, rank, world, multiple=1):
     return rank * per, (rank + 1) * per
 
 
+class _PeerSlabs:
+    """One fp32 receive buffer [world, rows, cols] per rank, each mapped into every
+    other rank of the node through CUDA IPC (plain peer mappings, no multicast
+    object).  Slab s of a rank's buffer is written by rank s only."""
+
+    def __init__(self, group, world, rank, rows, cols, device):
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.rows, self.cols = rows, cols
+        self.local = torch.empty((world, rows, cols), dtype=torch.float32, device=device)
+        handles = [None] * world
+        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
+        self.mapped = [self.local if r == rank else fn(*args) for r, (fn, args) in enumerate(handles)]
+        slab_bytes = rows * cols * 4
+        self.my_slab_on = [t.data_ptr() + rank * slab_bytes for t in self.mapped]
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+
+
+def _peer_access_ok(device, world):
+    if os.environ.get("MXQ_TP_FUSED_SCATTER", "1") == "0" or world > 8:
+        return False
+    me = device.index if device.index is not None else torch.cuda.current_device()
+    n = torch.cuda.device_count()
+    return n >= world and all(d == me or torch.cuda.can_device_access_peer(me, d) for d in range(world))
+
+
 class TensorParallelFFN(torch.nn.Module):
     def __init__(self, hidden, intermediate, mx_specs, group=None, eps=1e-5, device=None, dtype=torch.bfloat16):
         super().__init__()
@@ -56,6 +89,7 @@ class TensorParallelFFN(torch.nn.Module):
         self.w_up = torch.nn.Parameter(torch.empty(hi - lo, hidden, **kw))
         self.w_down = torch.nn.Parameter(torch.empty(hidden, hi - lo, **kw))
         self._packed = None
+        self._slabs = None
 
     @torch.no_grad()
     def load_full(self, w_gate, w_up, w_down, norm_weight=None):
@@ -138,9 +172,20 @@ class TensorParallelFFN(torch.nn.Module):
         if self.world == 1:
             return be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=h.dtype, bfloat_bits=bits,
                               round_mode=out_rnd)[0]
-        part = be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=torch.float32, bfloat_bits=0,
-                          round_mode=-1)[0]
-        out = self._reduce_scatter_rows(part)
+        rows = T // self.world
+        if self._slabs is None and _peer_access_ok(h.device, self.world):
+            self._slabs = _PeerSlabs(self.group, self.world, self.rank, rows, self.hidden, h.device)
+        sl = self._slabs
+        if sl is not None and (sl.rows, sl.cols) == (rows, self.hidden):
+            # GEMM + scatter in one kernel; the previous call's slabs were consumed before any rank
+            # could get past this call's all-gather, so they may be overwritten now
+            be.gemm_mx_scatter(ac, as_, dc, ds, sl.my_slab_on, rows, T, self.hidden, Il, ak, dk)
+            dist.all_reduce(sl.token, group=self.group)           # every rank's tiles have landed
+            out = be.sum_slabs(sl.local)
+        else:
+            part = be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=torch.float32, bfloat_bits=0,
+                              round_mode=-1)[0]
+            out = self._reduce_scatter_rows(part)
         out = quantize_elemwise_op(out, sp, round=sp["round_output"])
         return out.to(h.dtype)
 

@@ -147,3 +147,45 @@ def test_linear_fwd_composite_equals_two_calls(be):
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
         assert int(wsp[:4].view(torch.int32).item()) == 0
+
+
+@pytest.mark.parametrize("n_dests,rows_per_dest,M", [(2, 256, 512), (4, 128, 512), (3, 256, 700), (1, 384, 384)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_scatter_equals_plain_gemm(be, n_dests, rows_per_dest, M, tile_n):
+    """The scattering GEMM stores rows [d*R, (d+1)*R) into destination d: same values, bit for bit, as the
+    plain GEMM (here all destinations are buffers on the same GPU); rows past M are left untouched."""
+    N, K = 384, 256
+    g = torch.Generator().manual_seed(11)
+    A = (torch.randn(M, K, generator=g) * 2).to(torch.bfloat16).cuda()
+    B = (torch.randn(N, K, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    _, ca, sa, ka = quant_operand(be, A, "fp8_e4m3", M)
+    _, cb, sb, kb = quant_operand(be, B, "fp4_e2m1", N)
+    want = be.gemm_mx(ca, sa, cb, sb, 1, M, N, K, ka, kb, torch.float32, 0, -1, None, tile_n)[0]
+    dests = [torch.full((rows_per_dest, N), -7.0, dtype=torch.float32, device="cuda") for _ in range(n_dests)]
+    be.gemm_mx_scatter(ca, sa, cb, sb, [d.data_ptr() for d in dests], rows_per_dest, M, N, K, ka, kb, tile_n=tile_n)
+    torch.cuda.synchronize()
+    assert be.device_status() == 0
+    got = torch.cat(dests, 0)
+    assert torch.equal(got[:M], want)
+    assert bool((got[M:] == -7.0).all())
+
+
+def test_gemm_scatter_rejects_bad_arguments(be):
+    u8 = torch.zeros(128 * 128, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(512, dtype=torch.uint8, device="cuda")
+    d = torch.zeros(128, 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(be.MxqError):          # rows per destination not a multiple of 128
+        be.gemm_mx_scatter(u8, sf, u8, sf, [d.data_ptr()], 100, 128, 128, 128)
+    with pytest.raises(be.MxqError):          # more rows than the destinations hold
+        be.gemm_mx_scatter(u8, sf, u8, sf, [d.data_ptr()], 128, 256, 128, 128)
+    with pytest.raises(be.MxqError):          # too many destinations
+        be.gemm_mx_scatter(u8, sf, u8, sf, [d.data_ptr()] * 9, 128, 128, 128, 128)
+
+
+def test_sum_slabs_adds_in_order(be):
+    torch.manual_seed(2)
+    s = (torch.randn(5, 300, 64, device="cuda") * torch.tensor([1e8, 1.0, -1e8, 3.0, 1e-3], device="cuda").view(5, 1, 1))
+    want = s[0]
+    for k in range(1, 5):
+        want = want + s[k]
+    assert torch.equal(be.sum_slabs(s.contiguous()), want)
