@@ -52,6 +52,19 @@ const char* mxq_status_string(int status);
 int mxq_version(void);
 
 /*
+ * Device buffers shared between the processes of one node (no reference
+ * counterpart), the destinations of mxq_gemm_mx_scatter.  mxq_peer_alloc
+ * allocates `bytes` on the current device and fills a 64-byte handle another
+ * process passes to mxq_peer_open WITH ITS OWN DEVICE CURRENT; the pointer it
+ * gets is valid for kernels of that device.  Close every mapping before the
+ * owner frees the buffer.
+ */
+int mxq_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int mxq_peer_free(void* ptr);
+int mxq_peer_open(const void* handle64, void** ptr);
+int mxq_peer_close(void* ptr);
+
+/*
  * MX block fake-quantization, optionally also emitting the packed operand.
  * Replaces quantize_mx_by_tile_func_cuda (mx/cpp/funcs.cpp:177-197) and
  * quantize_mx_func_cuda (funcs.cpp:154-175; the caller no longer computes the

@@ -272,13 +272,48 @@ def gemm_mx_scatter(a_codes, a_scales, b_codes, b_scales, dest_ptrs, rows_per_de
                                         int(bfloat_bits), int(round_mode), int(tile_n), _stream(a_codes)))
 
 
-def sum_slabs(slabs):
-    """slabs [n, ...] fp32 -> their sum over dim 0, added in order; see mxq_sum_slabs_f32."""
-    if not (slabs.is_cuda and slabs.is_contiguous() and slabs.dtype == torch.float32):
-        raise MxqError("slabs must be a contiguous float32 CUDA tensor")
-    out = torch.empty(slabs.shape[1:], dtype=torch.float32, device=slabs.device)
-    with _device_of(slabs.device):
-        check(lib().mxq_sum_slabs_f32(_ptr(slabs), slabs.shape[0], out.numel(), _ptr(out), _stream(slabs)))
+def peer_alloc(device, nbytes):
+    """(device pointer, 64-byte handle) of a fresh buffer other processes can map; see mxq_peer_alloc."""
+    L = lib()
+    ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    L.mxq_peer_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+    with _device_of(device):
+        check(L.mxq_peer_alloc(int(nbytes), ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_open(device, handle):
+    """Map another process's buffer for kernels of `device`; see mxq_peer_open."""
+    L = lib()
+    ptr = ctypes.c_void_p()
+    L.mxq_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    with _device_of(device):
+        check(L.mxq_peer_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ptr):
+    lib().mxq_peer_close.argtypes = [ctypes.c_void_p]
+    return lib().mxq_peer_close(ptr)
+
+
+def peer_free(ptr):
+    lib().mxq_peer_free.argtypes = [ctypes.c_void_p]
+    return lib().mxq_peer_free(ptr)
+
+
+def sum_slabs(slabs, n_slabs=None, shape=None, device=None):
+    """Sum of n fp32 slabs, added in order; see mxq_sum_slabs_f32.  `slabs` is a contiguous
+    float32 CUDA tensor [n, ...] or a raw device pointer (then n_slabs, shape and device are required)."""
+    if isinstance(slabs, int):
+        ptr = slabs
+    else:
+        if not (slabs.is_cuda and slabs.is_contiguous() and slabs.dtype == torch.float32):
+            raise MxqError("slabs must be a contiguous float32 CUDA tensor")
+        ptr, n_slabs, shape, device = _ptr(slabs), slabs.shape[0], tuple(slabs.shape[1:]), slabs.device
+    out = torch.empty(shape, dtype=torch.float32, device=device)
+    with _device_of(out.device):
+        check(lib().mxq_sum_slabs_f32(ptr, int(n_slabs), out.numel(), _ptr(out), _stream(out)))
     return out
 
 

@@ -1,5 +1,6 @@
 // Status strings and version of the C ABI.
 #include "mxq_common.cuh"
+#include <string.h>
 
 extern "C" const char* mxq_status_string(int status) {
     switch (status) {
@@ -14,3 +15,39 @@ extern "C" const char* mxq_status_string(int status) {
     }
 }
 extern "C" int mxq_version(void) { return 1; }
+
+// ---------------------------------------------------------------------------
+// Receive buffers that other processes of the node can map (CUDA IPC).  The
+// importing process opens the handle while ITS OWN device is current, which is
+// what makes the mapping usable by kernels of that device (peer access between
+// the two GPUs is enabled by the open call); a mapping opened under the owner's
+// device index is only good for kernels launched on that device.
+// ---------------------------------------------------------------------------
+extern "C" int mxq_peer_alloc(int64_t bytes, void** ptr, void* handle64) {
+    if (bytes <= 0 || !ptr || !handle64) return MXQ_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) { cudaGetLastError(); return MXQ_ERR_CUDA; }
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaGetLastError(); cudaFree(p); return MXQ_ERR_CUDA; }
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return MXQ_OK;
+}
+extern "C" int mxq_peer_free(void* ptr) {
+    if (!ptr) return MXQ_OK;
+    return cudaFree(ptr) == cudaSuccess ? MXQ_OK : MXQ_ERR_CUDA;
+}
+extern "C" int mxq_peer_open(const void* handle64, void** ptr) {
+    if (!handle64 || !ptr) return MXQ_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return MXQ_ERR_CUDA; }
+    *ptr = p;
+    return MXQ_OK;
+}
+extern "C" int mxq_peer_close(void* ptr) {
+    if (!ptr) return MXQ_OK;
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? MXQ_OK : MXQ_ERR_CUDA;
+}

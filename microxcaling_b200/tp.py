@@ -50,19 +50,35 @@ def shard_bounds(n, rank, world, multiple=1):
 
 class _PeerSlabs:
     """One fp32 receive buffer [world, rows, cols] per rank, each mapped into every
-    other rank of the node through CUDA IPC (plain peer mappings, no multicast
-    object).  Slab s of a rank's buffer is written by rank s only."""
+    other rank of the node through CUDA IPC (plain peer mappings opened under the
+    importer's own device, no multicast object).  Slab s of a rank's buffer is
+    written by rank s only."""
 
     def __init__(self, group, world, rank, rows, cols, device):
-        from torch.multiprocessing.reductions import reduce_tensor
-        self.rows, self.cols = rows, cols
-        self.local = torch.empty((world, rows, cols), dtype=torch.float32, device=device)
-        handles = [None] * world
-        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
-        self.mapped = [self.local if r == rank else fn(*args) for r, (fn, args) in enumerate(handles)]
+        from . import _backend as be
+        self.rows, self.cols, self.world, self.device = rows, cols, world, device
         slab_bytes = rows * cols * 4
-        self.my_slab_on = [t.data_ptr() + rank * slab_bytes for t in self.mapped]
+        self.local, handle = be.peer_alloc(device, world * slab_bytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self.opened = [None if r == rank else be.peer_open(device, h) for r, h in enumerate(handles)]
+        self.my_slab_on = [(self.local if r == rank else p) + rank * slab_bytes for r, p in enumerate(self.opened)]
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def close(self):
+        """Collective in spirit: every rank closes its mappings before any owner frees its buffer
+        (call it on all ranks, with a barrier in between if the ranks are not already in step)."""
+        from . import _backend as be
+        for p in self.opened:
+            if p is not None:
+                be.peer_close(p)
+        self.opened = []
+
+    def free(self):
+        from . import _backend as be
+        if self.local:
+            be.peer_free(self.local)
+            self.local = None
 
 
 def _peer_access_ok(device, world):
@@ -90,6 +106,16 @@ class TensorParallelFFN(torch.nn.Module):
         self.w_down = torch.nn.Parameter(torch.empty(hidden, hi - lo, **kw))
         self._packed = None
         self._slabs = None
+
+    def release_peer_buffers(self):
+        """Unmap and free the receive buffers of the scattering GEMM (all ranks call this together)."""
+        if self._slabs is not None:
+            torch.cuda.synchronize()
+            self._slabs.close()
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self._slabs.free()
+            self._slabs = None
 
     @torch.no_grad()
     def load_full(self, w_gate, w_up, w_down, norm_weight=None):
@@ -181,7 +207,7 @@ class TensorParallelFFN(torch.nn.Module):
             # could get past this call's all-gather, so they may be overwritten now
             be.gemm_mx_scatter(ac, as_, dc, ds, sl.my_slab_on, rows, T, self.hidden, Il, ak, dk)
             dist.all_reduce(sl.token, group=self.group)           # every rank's tiles have landed
-            out = be.sum_slabs(sl.local)
+            out = be.sum_slabs(sl.local, self.world, (rows, self.hidden), h.device)
         else:
             part = be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=torch.float32, bfloat_bits=0,
                               round_mode=-1)[0]

@@ -35,6 +35,7 @@ def main():
         full = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(full, y)
         outs[fused] = torch.cat(full, 0).float()
+        ffn.release_peer_buffers()
     # the unsharded block, on a one-rank group of this process
     os.environ["MXQ_TP_FUSED_SCATTER"] = "0"
     solo_groups = [dist.new_group([r]) for r in range(world)]
