@@ -166,10 +166,29 @@ int mxq_reduce_max_inner(const void* in, void* out, int64_t rows, int64_t inner,
  *   calls, whose summation order is unspecified).  bias, x_norm [rows, hidden]
  *   and rms_inv [rows] may be NULL.  hidden % 8 == 0 needs 16-byte aligned
  *   pointers; other widths take an element-wise path.
+ * mxq_softmax_bf16: SoftmaxFunction.forward over the last dimension (mx/softmax.py:18-41)
+ *   m = max(x); d = x - m; e = exp(d) (exp2(d) if use_exp2); s = sum(e); out = e / s;
+ *   the row sum is accumulated in fp32 and rounded once.  cols % 8 == 0, cols <= 2048
+ *   (MXQ_ERR_UNSUPPORTED otherwise), 16-byte aligned pointers.
  */
+int mxq_softmax_bf16(const void* x, void* out, int64_t rows, int64_t cols, int use_exp2, void* stream);
 int mxq_silu_bf16(const void* gate, const void* up, void* out, void* sig, int64_t n, void* stream);
 int mxq_rmsnorm_bf16(const void* x, const void* weight, const void* bias, void* out, void* x_norm,
                      void* rms_inv, int64_t rows, int64_t hidden, float eps, void* stream);
+
+/*
+ * SiLU(gate) * up (the chain of mxq_silu_bf16) fused into the MX packing of the
+ * product along its last axis: what mxq_silu_bf16 followed by mxq_quantize_mx
+ * (codes + scales, no dequantized output) writes, without the bfloat16 product
+ * ever reaching memory.  gate, up: bfloat16 [rows, K], K % 32 == 0, block 32;
+ * fp element formats with a one-byte container; rmode nearest / floor / even;
+ * flags: MXQ_SCALES_GEMM_LAYOUT or 0.  Replaces, for the gated feed-forward block,
+ * silu + simd_mul + the quantize_mx_op of the down projection's input
+ * (mx/activations.py:418-439, mx/simd_ops.py:189-237, mx/linear.py:75-83).
+ */
+int mxq_swiglu_quantize_mx(const void* gate, const void* up, void* codes, void* scales, int64_t rows, int64_t K,
+                           int scale_bits, int elem_ebits, int elem_mbits, float elem_max_norm,
+                           int flush_fp32_subnorms, int rmode, int flags, int64_t sf_rows_per_batch, void* stream);
 
 /*
  * Block-scaled MX GEMM on the tensor cores (tcgen05 kind::mxf8f6f4):

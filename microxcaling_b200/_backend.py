@@ -55,6 +55,8 @@ def lib():
         L.mxq_reduce_sum_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_reduce_max_inner.argtypes = [vp, vp, i64, i64, vp]
         L.mxq_silu_bf16.argtypes = [vp, vp, vp, vp, i64, vp]
+        L.mxq_softmax_bf16.argtypes = [vp, vp, i64, i64, i32, vp]
+        L.mxq_swiglu_quantize_mx.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, f32, i32, i32, i32, i64, vp]
         L.mxq_gemm_mx_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i32, i32, i32,
                                           i32, i32, i32, vp]
         L.mxq_sum_slabs_f32.argtypes = [vp, i32, i64, vp, vp]
@@ -354,6 +356,40 @@ def silu_bf16(gate, up=None, want_sig=False):
     with _device_of(gate.device):
         check(lib().mxq_silu_bf16(_ptr(gate), _ptr(up), _ptr(out), _ptr(sig), gate.numel(), _stream(gate)))
     return (out, sig) if want_sig else out
+
+
+def swiglu_quantize_mx(gate, up, scale_bits, ebits, mbits, max_norm, flush=False, rmode=0, gemm_layout=True):
+    """Packed MX operand (codes uint8 [rows, K], scales uint8) of SiLU(gate) * up; see mxq_swiglu_quantize_mx."""
+    _require_bf16(gate, "gate")
+    _require_bf16(up, "up")
+    if gate.dim() != 2 or up.shape != gate.shape:
+        raise MxqError("gate and up must be [rows, K] tensors of the same shape")
+    rows, K = gate.shape
+    codes = torch.empty((rows, K), dtype=torch.uint8, device=gate.device)
+    if gemm_layout:
+        alloc = torch.empty if rows % 128 == 0 and K % 128 == 0 else torch.zeros
+        scales = alloc(((rows + 127) // 128) * ((K + 127) // 128) * 512, dtype=torch.uint8, device=gate.device)
+    else:
+        scales = torch.empty((rows, K // 32), dtype=torch.uint8, device=gate.device)
+    with _device_of(gate.device):
+        check(lib().mxq_swiglu_quantize_mx(_ptr(gate), _ptr(up), _ptr(codes), _ptr(scales), rows, K, int(scale_bits),
+                                           int(ebits), int(mbits), float(max_norm), int(bool(flush)), int(rmode),
+                                           SCALES_GEMM_LAYOUT if gemm_layout else 0, rows, _stream(gate)))
+    return codes, scales
+
+
+SOFTMAX_MAX_COLS = 2048
+
+
+def softmax_bf16(x, use_exp2=False):
+    """Fused bfloat16 softmax over the last dimension; see mxq_softmax_bf16."""
+    _require_bf16(x, "x")
+    cols = x.shape[-1]
+    out = torch.empty_like(x)
+    with _device_of(x.device):
+        check(lib().mxq_softmax_bf16(_ptr(x), _ptr(out), x.numel() // cols if cols else 0, cols, int(bool(use_exp2)),
+                                     _stream(x)))
+    return out
 
 
 def rmsnorm_bf16(x, weight, bias, eps, want_saved=False):

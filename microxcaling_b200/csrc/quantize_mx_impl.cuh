@@ -18,6 +18,7 @@
 // domain, the add-subtract grid rounding of mxq_math.cuh, one multiply back.
 #pragma once
 #include "mxq_common.cuh"
+#include "vector_math.cuh"
 #include <algorithm>
 #include <cstring>
 
@@ -43,6 +44,7 @@ struct FastDiv {
 
 struct MxArgs {
     const void* in;
+    const void* in2;        // second input of a fused prologue (SiLU(in) * in2), else unused
     void* out;
     uint8_t* codes;
     uint8_t* scales;
@@ -464,9 +466,14 @@ constexpr int kLastBfUnroll = 4;
 // elements is shared by `lanes_per_block` neighbouring lanes.  `row_local`: every
 // warp's 32 blocks lie in one row of the GEMM scale layout (4 lanes per block and
 // a multiple of 32 blocks per row), so the scale index is computed once per thread.
-template <int MODE, bool WANT_DQ, int CK>
+// PRO = 1: the value that is quantized is SiLU(in) * in2, computed per element
+// as the bfloat16 vector chain of the gated feed-forward block (silu_chain, then
+// the product, each step rounded to bfloat16) instead of being loaded: the
+// activation tensor is never written to memory.  Codes and scales only.
+template <int MODE, bool WANT_DQ, int CK, int PRO = 0>
 __global__ void __launch_bounds__(kLastBfThreads)
 mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block, const int row_local) {
+    static_assert(PRO == 0 || (!WANT_DQ && CK != CK_NONE), "the fused prologue produces the packed operand only");
     const int lane_shift = 31 - __clz(lanes_per_block);
     const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll) +
                          (threadIdx.x >> 5) * (32 * kLastBfUnroll) + (threadIdx.x & 31);
@@ -477,6 +484,24 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
         const int64_t v = base + u * 32;
         live[u] = v < nvec;
         raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in) + v) : make_uint4(0, 0, 0, 0);
+    }
+    if (PRO == 1) {
+#pragma unroll
+        for (int u = 0; u < kLastBfUnroll; ++u) {
+            const int64_t v = base + u * 32;
+            const uint4 up4 = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in2) + v) : make_uint4(0, 0, 0, 0);
+            const uint32_t g[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            const uint32_t up[4] = {up4.x, up4.y, up4.z, up4.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float s0, y0, s1, y1;
+                silu_chain(bf_lo(g[i]), s0, y0);
+                silu_chain(bf_hi(g[i]), s1, y1);
+                o[i] = pack_bf(rb(y0 * bf_lo(up[i])), rb(y1 * bf_hi(up[i])));
+            }
+            raw[u] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
     }
     int64_t sidx0 = 0;
     if (CK != CK_NONE && row_local) sidx0 = scale_index_last(a, (uint32_t)(base >> 2));
@@ -494,9 +519,23 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
             a.scales[sidx] = (uint8_t)(fb.ok ? fb.E : (uint32_t)scale_exp_from_absmax(m << 16, a.fmt.emax_elem, a.scale_emax));
         }
         if (!fb.ok) {
-            if (live[u])
+            if (PRO == 1) {
+                // the values exist only in registers: scaled-domain rounding of the 8 elements, unrolled
+                if (live[u]) {
+                    const BlockScale bs = block_scale(m << 16, a);
+                    uint32_t c[2] = {0, 0};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t xb = (i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16);
+                        const float q = quant_abs<MODE>(xb, bs, a.fmt);
+                        c[i >> 2] |= (code_pair<CK>(q, 0.f, xb >> 16) & 0xffu) << (8 * (i & 3));
+                    }
+                    reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
+                }
+            } else if (live[u]) {
                 bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, m << 16,
                                           StridedBytes{CK != CK_NONE ? a.codes + v * 8 : nullptr, 1}, 8);
+            }
             continue;
         }
         const uint32_t mp = a.fp_mp_base + fb.E * 0x00800080u;

@@ -11,27 +11,12 @@
 // its inputs once and writes its outputs once: HBM-bound streaming kernels,
 // 16-byte accesses, grid sized from the SM count.
 #include "mxq_common.cuh"
+#include "vector_math.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
+#include <math_constants.h>
 
 namespace mxq {
-
-__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-// fp32 -> nearest-even bfloat16, as a float
-__device__ __forceinline__ float rb(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
-__device__ __forceinline__ uint32_t pack_bf(float lo, float hi) {
-    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);   // both already on the bf16 grid
-}
-
-// sigmoid and SiLU of one bfloat16 value q with every intermediate rounded to
-// bfloat16: e = exp(-q), a = e + 1, s = 1 / a, y = q * s  (mx/activations.py:428-434)
-__device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
-    const float e = rb(expf(-q));
-    const float a = rb(e + 1.0f);
-    s = rb(__frcp_rn(a));                 // correctly rounded, hence equal to 1.0f / a
-    y = rb(q * s);
-}
 
 constexpr int kVecThreads = 256;
 
@@ -160,6 +145,68 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
     }
 }
 
+// Softmax over the last dimension, one warp per row kept in registers
+// (mx/softmax.py:18-41): m = max(x), d = x - m, e = exp(d) (or exp2), s = sum(e),
+// y = e / s with a bfloat16 rounding after every step; the row sum is accumulated
+// in fp32 and rounded once.  Rows of up to kSmMaxVec * 256 elements.
+constexpr int kSmThreads = 256;
+constexpr int kSmMaxVec = 8;
+
+__device__ __forceinline__ float nan_max(float a, float b) { return (b > a || b != b) ? b : a; }   // NaN wins, like torch.max
+
+template <bool EXP2>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const int64_t rows, const int cols) {
+    const int lane = threadIdx.x & 31;
+    const int nchunk = cols >> 3;
+    const int64_t warps = (int64_t)gridDim.x * (kSmThreads / 32);
+    for (int64_t row = (int64_t)blockIdx.x * (kSmThreads / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+        uint32_t w[kSmMaxVec][4];
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int k = 0; k < kSmMaxVec; ++k) {
+            const int c = lane + 32 * k;
+            if (c < nchunk) {
+                const uint4 v = __ldg(xr + c);
+                w[k][0] = v.x; w[k][1] = v.y; w[k][2] = v.z; w[k][3] = v.w;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { m = nan_max(m, bf_lo(w[k][i])); m = nan_max(m, bf_hi(w[k][i])); }
+            }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, s));
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < kSmMaxVec; ++k) {
+            if (lane + 32 * k < nchunk) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float d0 = rb(bf_lo(w[k][i]) - m), d1 = rb(bf_hi(w[k][i]) - m);
+                    const float e0 = rb(EXP2 ? exp2f(d0) : expf(d0)), e1 = rb(EXP2 ? exp2f(d1) : expf(d1));
+                    acc += e0;
+                    acc += e1;
+                    w[k][i] = pack_bf(e0, e1);
+                }
+            }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+        const float sum = rb(acc);
+        uint4* orow = reinterpret_cast<uint4*>(out + row * cols);
+#pragma unroll
+        for (int k = 0; k < kSmMaxVec; ++k) {
+            const int c = lane + 32 * k;
+            if (c < nchunk) {
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = pack_bf(rb(__fdiv_rn(bf_lo(w[k][i]), sum)), rb(__fdiv_rn(bf_hi(w[k][i]), sum)));
+                orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+}
+
 }  // namespace mxq
 
 extern "C" int mxq_silu_bf16(const void* gate, const void* up, void* out, void* sig, int64_t n, void* stream) {
@@ -194,5 +241,20 @@ extern "C" int mxq_rmsnorm_bf16(const void* x, const void* weight, const void* b
     rmsnorm_bf16_kernel<<<grid, kNormThreads, 0, (cudaStream_t)stream>>>(
         (const uint16_t*)x, (const uint16_t*)weight, (const uint16_t*)bias, (uint16_t*)out, (uint16_t*)x_norm,
         (uint16_t*)rms_inv, rows, hidden, 1.0f / (float)hidden, eps);
+    return check_launch();
+}
+
+extern "C" int mxq_softmax_bf16(const void* x, void* out, int64_t rows, int64_t cols, int use_exp2, void* stream) {
+    using namespace mxq;
+    if (rows < 0 || cols < 0) return MXQ_ERR_BAD_ARG;
+    if (rows == 0 || cols == 0) return MXQ_OK;
+    if (!x || !out) return MXQ_ERR_BAD_ARG;
+    if (cols % 8 != 0 || cols > kSmMaxVec * 256) return MXQ_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(out)) return MXQ_ERR_ALIGN;
+    const int64_t ctas = (rows + kSmThreads / 32 - 1) / (kSmThreads / 32);
+    const unsigned grid = (unsigned)std::min<int64_t>(ctas, (int64_t)sm_count() * 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (use_exp2) softmax_bf16_kernel<true><<<grid, kSmThreads, 0, st>>>((const uint16_t*)x, (uint16_t*)out, rows, (int)cols);
+    else softmax_bf16_kernel<false><<<grid, kSmThreads, 0, st>>>((const uint16_t*)x, (uint16_t*)out, rows, (int)cols);
     return check_launch();
 }

@@ -4,10 +4,11 @@ import torch
 import torch.nn.functional as F
 
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
-from .vector_ops import vec_div, vec_exp, vec_exp2, vec_mul, vec_quantize, vec_reduce_sum, vec_sub
+from .vector_ops import fused_bf16_ok, vec_div, vec_exp, vec_exp2, vec_mul, vec_quantize, vec_reduce_sum, vec_sub
 
 f_softmax = F.softmax
 LN_2_BF16 = 0.69140625
+_SOFTMAX_FUSED_MAX_COLS = 2048      # row length the one-warp-per-row kernel keeps in registers
 
 
 class SoftmaxFunction(torch.autograd.Function):
@@ -16,11 +17,16 @@ class SoftmaxFunction(torch.autograd.Function):
         dim = dim + input.dim() if dim < 0 else dim
         ctx.dim = dim
         rnd = mx_specs["round"]
-        x = vec_quantize(input, mx_specs=mx_specs)
-        x = vec_sub(x, x.max(dim, keepdim=True)[0], mx_specs=mx_specs, round=rnd)
-        e = (vec_exp2 if mx_specs.get("softmax_exp2", False) else vec_exp)(x, mx_specs=mx_specs, round=rnd)
-        s = vec_reduce_sum(e, dim, keepdim=True, mx_specs=mx_specs, round=rnd)
-        out = vec_div(e, s, mx_specs=mx_specs, round=rnd)
+        if dim == input.dim() - 1 and fused_bf16_ok(mx_specs, input) and input.shape[-1] % 8 == 0 \
+                and 0 < input.shape[-1] <= _SOFTMAX_FUSED_MAX_COLS:
+            from . import _backend
+            out = _backend.softmax_bf16(input.contiguous(), mx_specs.get("softmax_exp2", False))
+        else:
+            x = vec_quantize(input, mx_specs=mx_specs)
+            x = vec_sub(x, x.max(dim, keepdim=True)[0], mx_specs=mx_specs, round=rnd)
+            e = (vec_exp2 if mx_specs.get("softmax_exp2", False) else vec_exp)(x, mx_specs=mx_specs, round=rnd)
+            s = vec_reduce_sum(e, dim, keepdim=True, mx_specs=mx_specs, round=rnd)
+            out = vec_div(e, s, mx_specs=mx_specs, round=rnd)
         ctx.save_for_backward(out)
         ctx.mx_specs = get_backwards_mx_specs(mx_specs)
         return out

@@ -189,12 +189,17 @@ class TensorParallelFFN(torch.nn.Module):
                           round_mode=out_rnd)[0]
         up = be.gemm_mx(xc, xs, uc, us, 1, T, Il, self.hidden, xk, uk, out_dtype=h.dtype, bfloat_bits=bits,
                         round_mode=out_rnd)[0]
-        if fused_bf16_ok(sp, gate, up):
-            act = be.silu_bf16(gate, up)                      # SiLU(gate) * up, one pass
+        if fused_bf16_ok(sp, gate, up) and Il % 32 == 0 and sp["round_output"] in ("nearest", "floor", "even"):
+            # SiLU(gate) * up and the MX packing of the product in one pass; the vector format leaves
+            # bfloat16 values untouched, so the rounding between the two steps is the identity
+            eb, mb, _, mn, _ = _get_format_params(af)
+            ac, as_ = be.swiglu_quantize_mx(gate, up, sp["scale_bits"] or 8, eb, mb, mn, sp["mx_flush_fp32_subnorms"],
+                                            _MODE[rnd])
+            ak = 1 if eb == 5 else 0
         else:
             act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
-        act = quantize_elemwise_op(act, sp, round=sp["round_output"])
-        ac, as_, ak = _pack(act, af, sp, rnd, True)
+            act = quantize_elemwise_op(act, sp, round=sp["round_output"])
+            ac, as_, ak = _pack(act, af, sp, rnd, True)
         if self.world == 1:
             return be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=h.dtype, bfloat_bits=bits,
                               round_mode=out_rnd)[0]

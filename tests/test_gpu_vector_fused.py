@@ -25,8 +25,9 @@ SP = finalize_mx_specs({"bfloat": 16})
 def composed(monkeypatch, fn):
     """Run fn with the fused kernels switched off."""
     with monkeypatch.context() as m:
-        from microxcaling_b200 import activations, layernorm, tp
-        for mod in (activations, layernorm, tp):
+        import importlib
+        for name in ("activations", "layernorm", "softmax", "tp"):
+            mod = importlib.import_module("microxcaling_b200." + name)
             m.setattr(mod, "fused_bf16_ok", lambda *a, **k: False)
         return fn()
 
@@ -95,6 +96,35 @@ def test_rmsnorm(monkeypatch, rows, hidden):
     assert bool(((got - want).abs() <= 2 * ulp).all())
 
 
+@pytest.mark.parametrize("shape", [(4, 64, 2048), (300, 8), (33, 1000), (7, 3, 136)])
+@pytest.mark.parametrize("exp2", [False, True])
+def test_softmax(monkeypatch, shape, exp2):
+    """One row sum of unspecified order, as in RMSNorm: almost all rows identical, the rest within 2 ulp."""
+    sp = finalize_mx_specs({"bfloat": 16, "softmax_exp2": exp2})
+    torch.manual_seed(sum(shape))
+    x = (torch.randn(*shape, device="cuda") * 3).to(torch.bfloat16)
+    x.view(-1, shape[-1])[0, :3] = float("-inf")
+    got = mx.softmax(x, dim=-1, mx_specs=sp).float().view(-1, shape[-1])
+    want = composed(monkeypatch, lambda: mx.softmax(x, dim=-1, mx_specs=sp)).float().view(-1, shape[-1])
+    row_equal = (got == want).all(dim=1)
+    assert float(row_equal.float().mean()) >= 0.95, float(row_equal.float().mean())
+    ulp = want.abs().clamp_min(1e-30) * 2.0 ** -7
+    assert bool(((got - want).abs() <= 2 * ulp).all())
+
+
+def test_softmax_nan_row_and_wide_rows_fall_back(monkeypatch):
+    x = torch.randn(4, 64, device="cuda").to(torch.bfloat16)
+    x[1, 5] = float("nan")
+    got = mx.softmax(x, dim=-1, mx_specs=SP).float()
+    want = composed(monkeypatch, lambda: mx.softmax(x, dim=-1, mx_specs=SP)).float()
+    assert bool(got[1].isnan().all()) and bool(want[1].isnan().all())
+    assert same(got[[0, 2, 3]], want[[0, 2, 3]]) or bool(((got - want)[[0, 2, 3]].abs() <= want[[0, 2, 3]].abs() * 2.0 ** -6).all())
+    wide = torch.randn(2, 4096, device="cuda").to(torch.bfloat16)          # longer than the fused kernel takes
+    assert same(mx.softmax(wide, dim=-1, mx_specs=SP), composed(monkeypatch, lambda: mx.softmax(wide, dim=-1, mx_specs=SP)))
+    other = torch.randn(16, 8, 24, device="cuda").to(torch.bfloat16)       # not the last dimension
+    assert same(mx.softmax(other, dim=1, mx_specs=SP), composed(monkeypatch, lambda: mx.softmax(other, dim=1, mx_specs=SP)))
+
+
 def test_rmsnorm_backward_matches_composed(monkeypatch):
     torch.manual_seed(5)
     x = torch.randn(48, 512, device="cuda").to(torch.bfloat16)
@@ -127,3 +157,26 @@ def test_ffn_block_fused_equals_composed(monkeypatch):
     want = composed(monkeypatch, lambda: ffn(x)).float()
     row_equal = (got == want).all(dim=1)
     assert float(row_equal.float().mean()) >= 0.95
+
+
+@pytest.mark.parametrize("fmt", ["fp8_e4m3", "fp8_e5m2", "fp6_e3m2", "fp4_e2m1"])
+@pytest.mark.parametrize("rnd", [0, 1, 2])
+@pytest.mark.parametrize("gemm_layout", [False, True])
+def test_swiglu_quantize_equals_two_steps(fmt, rnd, gemm_layout):
+    """SiLU x up fused into the MX packing == mxq_silu_bf16 followed by mxq_quantize_mx, byte for byte;
+    the input walks every bf16 pattern (NaN / Inf / huge / tiny blocks take the slow path)."""
+    import oracle
+    from microxcaling_b200 import _backend as be
+    eb, mb, mn = oracle.FORMATS[fmt]
+    torch.manual_seed(4)
+    gate = all_bf16_patterns().reshape(256, 256)
+    up = (torch.randn(256, 256, device="cuda") * 3).to(torch.bfloat16)
+    up[7, :40] = 0
+    gate2 = torch.cat([gate, (torch.randn(128, 256, device="cuda") * 2).to(torch.bfloat16)])
+    up2 = torch.cat([up, (torch.randn(128, 256, device="cuda")).to(torch.bfloat16)])
+    act = be.silu_bf16(gate2, up2)
+    _, c_want, s_want = be.quantize_mx(act, 8, eb, mb, mn, 32, 1, False, rnd, want_dq=False, want_codes=True,
+                                       gemm_layout=gemm_layout, rows_per_batch=gate2.shape[0] if gemm_layout else 0)
+    c_got, s_got = be.swiglu_quantize_mx(gate2, up2, 8, eb, mb, mn, False, rnd, gemm_layout=gemm_layout)
+    assert torch.equal(c_got, c_want)
+    assert torch.equal(s_got.view(-1), s_want.view(-1))
