@@ -9,6 +9,8 @@ length not a multiple of 128) follows the reference's construction: fake-quantiz
 both operands, multiply with torch, round the result
 (mx/linear.py:62-96, mx/matmul.py:68-96, mx/bmm.py:40-62).
 """
+import weakref
+
 import torch
 
 from .elemwise_ops import quantize_elemwise_op
@@ -62,12 +64,36 @@ def _pack(x, fmt, specs, rnd, contraction_last):
     return codes, scales, (1 if ebits == 5 else 0)
 
 
-def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, trans1=False, trans2=False):
+# Packed right operands of inference calls, per source tensor: the reference re-quantizes a layer's
+# weight on every forward (mx/linear.py:40-47,83); with autograd off and the tensor unchanged since
+# the last call (same storage, same version counter, same format and rounding) the packed operand
+# is reused instead.  One entry per source tensor, dropped with it.
+_PACK_CACHE = weakref.WeakKeyDictionary()
+
+
+def _pack_cached(src, x, fmt, specs, rnd, contraction_last):
+    """_pack(x, ...) where x derives from the long-lived tensor `src` (a layer weight)."""
+    if src is None or torch.is_grad_enabled() or not x.is_cuda:
+        return _pack(x, fmt, specs, rnd, contraction_last)
+    key = (src.data_ptr(), src._version, x.dtype, tuple(x.shape), str(fmt), rnd, contraction_last, specs["scale_bits"],
+           specs["mx_flush_fp32_subnorms"], specs["bfloat"], specs["fp"], specs["round_weight"])
+    hit = _PACK_CACHE.get(src)
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    packed = _pack(x, fmt, specs, rnd, contraction_last)
+    _PACK_CACHE[src] = (key, packed)
+    return packed
+
+
+def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, trans1=False, trans2=False,
+            in2_source=None):
     """op1(in1) @ op2(in2), op(x) = x^T of the last two dims when trans is set.
 
     in1: [..., M, K] (or [..., K, M] with trans1); in2: [..., K, N] (or [..., N, K] with trans2),
     in2 may have fewer leading dims than in1 (a shared 2-D matrix).  `bias` is an
-    already-quantized vector added after the first output rounding."""
+    already-quantized vector added after the first output rounding.  `in2_source`: the
+    long-lived tensor in2 was derived from (a layer's weight), which lets inference calls
+    reuse its packed form."""
     fmt1, fmt2 = _fmt(fmt1), _fmt(fmt2)
     M, K = (in1.shape[-1], in1.shape[-2]) if trans1 else (in1.shape[-2], in1.shape[-1])
     N, K2 = (in2.shape[-2], in2.shape[-1]) if trans2 else (in2.shape[-1], in2.shape[-2])
@@ -82,7 +108,7 @@ def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, t
     if fast:
         from . import _backend as be
         a_codes, a_scales, ka = _pack(in1, fmt1, specs, round1, not trans1)
-        b_codes, b_scales, kb = _pack(in2, fmt2, specs, round2, trans2)
+        b_codes, b_scales, kb = _pack_cached(in2_source, in2, fmt2, specs, round2, trans2)
         if shared_b:
             batch, rows = 1, in1.numel() // K       # leading dims of in1 fold into M
             if rows != M:

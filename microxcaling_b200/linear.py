@@ -43,7 +43,7 @@ class LinearFunction(torch.autograd.Function):
             bf_weight = bf_weight.to(bf_in.dtype)
         output = mx_gemm(bf_in, bf_weight, mx_specs["a_elem_format"], mx_specs["w_elem_format"], mx_specs,
                          mx_specs["round_mx_output"], mx_specs["round_mx_output"], mx_specs["round_output"],
-                         bias=bf_bias, trans2=True)
+                         bias=bf_bias, trans2=True, in2_source=weight)
         ctx.mx_specs = get_backwards_mx_specs(mx_specs)
         ctx.prequantized_weights = prequantized_weights
         ctx.name = name

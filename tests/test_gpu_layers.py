@@ -131,3 +131,28 @@ def test_attention_shaped_bmm_softmax_bmm():
     o_cpu = mx.bmm(p, outs["cpu"][1], mx_specs=outs["cpu"][2])
     o_gpu = mx.bmm(p.cuda(), outs["cuda"][1], mx_specs=outs["cuda"][2])
     close_bf16(o_gpu, o_cpu.numpy(), "out")
+
+
+def test_packed_weight_is_reused_only_while_unchanged(monkeypatch):
+    """Inference calls reuse the packed weight of mx.Linear; an in-place update of the weight, a different
+    format, or autograd being on makes the layer pack it again."""
+    from microxcaling_b200 import _backend, _mxgemm
+    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16})
+    lin = mx.Linear(256, 128, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
+    x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
+    calls = []
+    real = _backend.quantize_mx
+    monkeypatch.setattr(_backend, "quantize_mx", lambda A, *a, **k: (calls.append(tuple(A.shape)), real(A, *a, **k))[1])
+    with torch.no_grad():
+        y1 = lin(x)
+        n1 = len(calls)
+        y2 = lin(x)
+        assert len(calls) - n1 == 1                 # only the activations were packed again
+        assert torch.equal(y1, y2)
+        lin.weight.mul_(2.0)
+        n2 = len(calls)
+        y3 = lin(x)
+        assert len(calls) - n2 == 2 and not torch.equal(y3, y1)
+    n3 = len(calls)
+    lin(x)                                          # autograd on: no reuse
+    assert len(calls) - n3 == 2
