@@ -65,23 +65,24 @@ def _pack(x, fmt, specs, rnd, contraction_last):
 
 
 # Packed right operands of inference calls, per source tensor: the reference re-quantizes a layer's
-# weight on every forward (mx/linear.py:40-47,83); with autograd off and the tensor unchanged since
+# weight on every forward (mx/linear.py:40-47,83); when nothing needs a gradient and the tensor is unchanged since
 # the last call (same storage, same version counter, same format and rounding) the packed operand
 # is reused instead.  One entry per source tensor, dropped with it.
-_PACK_CACHE = weakref.WeakKeyDictionary()
+_PACK_CACHE = {}          # id(source tensor) -> (weak reference, key, packed operand)
 
 
 def _pack_cached(src, x, fmt, specs, rnd, contraction_last):
     """_pack(x, ...) where x derives from the long-lived tensor `src` (a layer weight)."""
-    if src is None or torch.is_grad_enabled() or not x.is_cuda:
+    if src is None or not x.is_cuda:
         return _pack(x, fmt, specs, rnd, contraction_last)
     key = (src.data_ptr(), src._version, x.dtype, tuple(x.shape), str(fmt), rnd, contraction_last, specs["scale_bits"],
            specs["mx_flush_fp32_subnorms"], specs["bfloat"], specs["fp"], specs["round_weight"])
-    hit = _PACK_CACHE.get(src)
-    if hit is not None and hit[0] == key:
-        return hit[1]
+    sid = id(src)
+    hit = _PACK_CACHE.get(sid)
+    if hit is not None and hit[0]() is src and hit[1] == key:
+        return hit[2]
     packed = _pack(x, fmt, specs, rnd, contraction_last)
-    _PACK_CACHE[src] = (key, packed)
+    _PACK_CACHE[sid] = (weakref.ref(src, lambda _r, sid=sid: _PACK_CACHE.pop(sid, None)), key, packed)
     return packed
 
 
@@ -92,8 +93,8 @@ def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, t
     in1: [..., M, K] (or [..., K, M] with trans1); in2: [..., K, N] (or [..., N, K] with trans2),
     in2 may have fewer leading dims than in1 (a shared 2-D matrix).  `bias` is an
     already-quantized vector added after the first output rounding.  `in2_source`: the
-    long-lived tensor in2 was derived from (a layer's weight), which lets inference calls
-    reuse its packed form."""
+    long-lived tensor in2 was derived from (a layer's weight); callers pass it only for
+    inference calls, which may then reuse its packed form."""
     fmt1, fmt2 = _fmt(fmt1), _fmt(fmt2)
     M, K = (in1.shape[-1], in1.shape[-2]) if trans1 else (in1.shape[-2], in1.shape[-1])
     N, K2 = (in2.shape[-2], in2.shape[-1]) if trans2 else (in2.shape[-1], in2.shape[-2])

@@ -20,7 +20,8 @@ torch_matmul = torch.matmul
 
 class LinearFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None):
+    def forward(ctx, input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None,
+                inference=False):
         bf_in = quantize_elemwise_op(input, mx_specs=mx_specs, round=mx_specs["round_output"])
         if prequantized_weights:
             assert weight.dtype == torch.bfloat16
@@ -43,7 +44,8 @@ class LinearFunction(torch.autograd.Function):
             bf_weight = bf_weight.to(bf_in.dtype)
         output = mx_gemm(bf_in, bf_weight, mx_specs["a_elem_format"], mx_specs["w_elem_format"], mx_specs,
                          mx_specs["round_mx_output"], mx_specs["round_mx_output"], mx_specs["round_output"],
-                         bias=bf_bias, trans2=True, in2_source=weight)
+                         bias=bf_bias, trans2=True,
+                         in2_source=weight if inference else None)
         ctx.mx_specs = get_backwards_mx_specs(mx_specs)
         ctx.prequantized_weights = prequantized_weights
         ctx.name = name
@@ -96,7 +98,10 @@ def linear(input, weight, bias=None, mx_specs=None, prequantized_weights=False, 
     if mx_specs is None:
         return f_linear(input, weight, bias=bias)
     mx_specs = apply_mx_specs(mx_specs)
-    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name)
+    # nothing will be differentiated: the packed weight may be kept for the next call
+    inference = not torch.is_grad_enabled() or not (input.requires_grad or weight.requires_grad or
+                                                    (bias is not None and bias.requires_grad))
+    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name, inference)
 
 
 class Linear(torch.nn.Linear):
