@@ -107,7 +107,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one mx_strided_bf16_kernel launch on this workload
 # (profiles/mx_strided_bf16_kernel__c2_sweep.md)
-STRIDED_TRAFFIC_BYTES = 219_897_856
+STRIDED_TRAFFIC_BYTES = 223_612_672
 
 
 def mx_linear_block(torch, be, dev):
@@ -158,7 +158,7 @@ def mx_linear_block(torch, be, dev):
             "gemm_us": t_gemm * 1e6, "gemm_tflops": flop / t_gemm / 1e12,
             "fwd_bwd_us": t_step * 1e6, "fwd_bwd_tflops": 3 * flop / t_step / 1e12,
             "tensor_peak_nominal_tflops": 4500.0, "gemm_frac_of_nominal": flop / t_gemm / 1e12 / 4500.0,
-            "tensor_pipe_active_pct_ncu": 73.4,
+            "tensor_pipe_active_pct_ncu": 74.0,
             "note": "fwd_bwd counts the 3 GEMMs' flops over the whole step (6 MX quantizations included); "
                     "tensor_pipe_active_pct_ncu from profiles/gemm_mx_kernel__8192x4096x4096.md"}
 
@@ -199,11 +199,16 @@ def mx_ffn_block(torch, dist, dev, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     flop = 3 * 2.0 * T * H * I
+    fused_scatter = ffn._slabs is not None
+    ffn.release_peer_buffers()
     del ffn, x, y
     torch.cuda.empty_cache()
     return {"shape": "16384 tokens, hidden 8192, intermediate 28672, SwiGLU + RMSNorm, w fp4_e2m1 / a fp8_e4m3",
-            "parallelism": "tp%d (column-parallel gate/up, row-parallel down, NCCL all-gather of packed "
-                           "activations + reduce-scatter of fp32 partials)" % world,
+            "parallelism": "tp%d (column-parallel gate/up, row-parallel down; NCCL all-gather of packed activations; "
+                           "%s)" % (world, "single GPU, no exchange" if world == 1 else
+                                    "down-projection GEMM scatters its fp32 tiles into the owners' buffers over "
+                                    "peer memory, then an ordered slab sum" if fused_scatter else
+                                    "NCCL reduce-scatter of fp32 partials"),
             "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "scaling": "strong"}
 
 
