@@ -24,6 +24,7 @@
 #include <cuda.h>
 #include <algorithm>
 #include <cstring>
+#include <cstdlib>
 #include "mxq_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
@@ -116,6 +117,87 @@ __device__ __forceinline__ void tile_coords(int64_t t, const GemmArgs& g, int64_
     const int64_t rows = min((int64_t)kGroupM, g.m_tiles - grp * kGroupM);
     mt = grp * kGroupM + i % rows;
     nt = i / rows;
+}
+
+// Rounds one epilogue warp's share of an accumulator tile (kCols = BN / 2 columns of 32 rows,
+// already in registers) and stores it: 64-byte chunks through a swizzled staging tile and TMA
+// stores (which clip ragged edges), or plain stores when the row pitch is not a multiple of 16 bytes.
+template <int BN>
+__device__ __forceinline__ void round_and_store(const uint32_t* v, const int half, const int lane, const uint32_t stg,
+                                                const GemmArgs& g, const CUtensorMap* tmap_c, const int64_t row0,
+                                                const int64_t row0_dest, const int64_t nt, const int64_t bi) {
+    constexpr int kCols = BN / 2;
+    const bool f32_out = g.out_dtype == DT_F32;
+    const float* bp = reinterpret_cast<const float*>(g.bias);
+#pragma unroll
+    for (int cc = 0; cc < kCols; cc += 32) {
+        // 32 accumulator columns: one 64-byte chunk of bf16 or two of fp32
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+            if (!f32_out && sub == 1) break;
+            const int c0 = half * kCols + cc + sub * 16;
+            const int64_t col0 = nt * BN + c0;
+            if (col0 >= g.N) break;
+            uint32_t w[16];
+            if (f32_out) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    uint32_t b = round_out_bits(v[cc + sub * 16 + i], g.rnd);
+                    if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
+                    w[i] = b;
+                }
+            } else if (g.epi_kind == 0) {              // half away: add half an ulp of bf16, keep the upper halves
+#pragma unroll
+                for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i] + 0x8000u, v[cc + 2 * i + 1] + 0x8000u, 0x7632);
+            } else if (g.epi_kind == 1) {              // toward zero
+#pragma unroll
+                for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i], v[cc + 2 * i + 1], 0x7632);
+            } else if (g.epi_kind == 2) {              // half even: the hardware conversion
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[cc + 2 * i]), __uint_as_float(v[cc + 2 * i + 1]));
+                    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    uint32_t b0 = round_out_bits(v[cc + 2 * i], g.rnd);
+                    uint32_t b1 = round_out_bits(v[cc + 2 * i + 1], g.rnd);
+                    if (bp) {
+                        b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
+                        b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
+                    }
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b0), __uint_as_float(b1));
+                    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+            if (g.c_tma) {
+                if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                ptx::fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::tma_store_3d(tmap_c, stg, (int)col0, (int)row0_dest, (int)bi);
+                    ptx::bulk_commit();
+                }
+            } else if (row0 + lane < g.M) {
+                // row pitch not a multiple of 16 bytes: plain stores
+                const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (f32_out) {
+                        if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
+                    } else {
+                        if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
+                        if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
+                    }
+                }
+            }
+        }
+    }
 }
 
 template <int BN, int STAGES, int ACC_BUFS>
@@ -278,75 +360,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
             if (warp == 2 && lane == 0) TRACE(800 + 2 * tile_i);
-#pragma unroll
-            for (int cc = 0; cc < kCols; cc += 32) {
-                // 32 accumulator columns: one 64-byte chunk of bf16 or two of fp32
-#pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-                    if (!f32_out && sub == 1) break;
-                    const int c0 = half * kCols + cc + sub * 16;
-                    const int64_t col0 = nt * BN + c0;
-                    if (col0 >= g.N) break;
-                    uint32_t w[16];
-                    if (f32_out) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            uint32_t b = round_out_bits(v[cc + sub * 16 + i], g.rnd);
-                            if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
-                            w[i] = b;
-                        }
-                    } else if (g.epi_kind == 0) {              // half away: add half an ulp of bf16, keep the upper halves
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i] + 0x8000u, v[cc + 2 * i + 1] + 0x8000u, 0x7632);
-                    } else if (g.epi_kind == 1) {              // toward zero
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i], v[cc + 2 * i + 1], 0x7632);
-                    } else if (g.epi_kind == 2) {              // half even: the hardware conversion
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[cc + 2 * i]), __uint_as_float(v[cc + 2 * i + 1]));
-                            w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            uint32_t b0 = round_out_bits(v[cc + 2 * i], g.rnd);
-                            uint32_t b1 = round_out_bits(v[cc + 2 * i + 1], g.rnd);
-                            if (bp) {
-                                b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
-                                b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
-                            }
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b0), __uint_as_float(b1));
-                            w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                        }
-                    }
-                    if (g.c_tma) {
-                        if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
-                        __syncwarp();
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-                        ptx::fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            ptx::tma_store_3d(tmap_c, stg, (int)col0, (int)row0_dest, (int)bi);
-                            ptx::bulk_commit();
-                        }
-                    } else if (row0 + lane < g.M) {
-                        // row pitch not a multiple of 16 bytes: plain stores
-                        const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            if (f32_out) {
-                                if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
-                            } else {
-                                if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
-                                if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
-                            }
-                        }
-                    }
-                }
-            }
+            round_and_store<BN>(v, half, lane, stg, g, tmap_c, row0, row0_dest, nt, bi);
         }
         if (lane == 0) ptx::bulk_wait_all();
     }
@@ -358,6 +372,183 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair kernel (cta_group::2): two CTAs of a cluster share one 256 x 256
+// tile.  Each CTA stages its own 128 rows of A, its own 128-row half of the B
+// tile and the scales it needs (its rows of A, all 256 columns of B), so a K
+// block costs 33.5 KB of shared-memory fill per SM instead of 49.5 KB; the even
+// CTA issues tcgen05.cp / tcgen05.mma for both, and every CTA drains the 128
+// accumulator rows held in its own tensor memory.  Barriers: `full` lives in
+// the even CTA and counts the bytes of both CTAs' loads; `empty` and `acc_full`
+// exist in both CTAs and are signalled together by a multicast commit;
+// `acc_empty` lives in the even CTA and collects the epilogue warps of both.
+// No load is multicast.  All waits are bounded as in the single-CTA kernel.
+// ---------------------------------------------------------------------------
+constexpr int kPairBN = 256;
+template <int STAGES>
+struct PairSmem {
+    static constexpr int kA = kBM * kBK;                   // this CTA's rows of A
+    static constexpr int kB = 128 * kBK;                   // this CTA's half of the B tile
+    static constexpr int kAB = kA + kB;
+    static constexpr int kSF = 3 * kSfChunk;               // scales: A (own rows) + B (256 columns)
+    static constexpr int kStageBytes = kAB + kSF;          // bytes one CTA loads per K block
+    static constexpr int kSfOff = STAGES * kAB;
+    static constexpr int kStgOff = kSfOff + STAGES * kSF;  // per epilogue warp: [32 rows x 64 bytes]
+    static constexpr int kBarOff = kStgOff + kEpiWarps * 2048;
+    static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                    const __grid_constant__ OutMaps tmaps_c, const GemmArgs g) {
+    using S = PairSmem<STAGES>;
+    constexpr int BN = kPairBN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
+    uint64_t* full = bars;                       // [STAGES]  used in the even CTA
+    uint64_t* empty = bars + STAGES;             // [STAGES]  one per CTA
+    uint64_t* acc_full = bars + 2 * STAGES;      // one per CTA
+    uint64_t* acc_empty = acc_full + 1;          // used in the even CTA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();             // 0 = even CTA (issues the MMAs)
+    constexpr uint32_t kSfaCol = BN;
+    constexpr uint32_t kSfbCol = BN + 4;
+    constexpr uint32_t kTmemCols = 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
+        ptx::mbar_init(ptx::smem_u32(acc_full), 1);
+        ptx::mbar_init(ptx::smem_u32(acc_empty), 2 * kEpiWarps);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_arrive();                                    // both CTAs' barriers exist before anyone signals them
+    ptx::cluster_wait();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t tiles_per_batch = g.m_tiles * g.n_tiles;    // 256 x 256 tiles
+    const int64_t total_tiles = tiles_per_batch * g.batch;
+    const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one per CTA) ----------------
+        if (ptx::elect_one()) {
+            ptx::prefetch_tmap(&tmap_a);
+            ptx::prefetch_tmap(&tmap_b);
+            ptx::prefetch_tmap(&tmap_sfa);
+            ptx::prefetch_tmap(&tmap_sfb);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = pair; t < total_tiles && ok; t += n_pairs) {
+                int64_t bi, mt2, nt;
+                tile_coords(t, g, tiles_per_batch, bi, mt2, nt);
+                const int64_t mt = 2 * mt2 + rank;             // this CTA's 128-row tile
+                for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (it >= (uint32_t)STAGES && !ptx::mbar_wait(ptx::smem_u32(&empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
+                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&full[s]), 2 * S::kStageBytes);
+                    const uint32_t bar = ptx::mapa(ptx::smem_u32(&full[s]), 0);
+                    const uint32_t ab = ptx::smem_u32(smem + (size_t)s * S::kAB);
+                    const uint32_t sf = ptx::smem_u32(smem + S::kSfOff + (size_t)s * S::kSF);
+                    ptx::tma_load_3d_pair(ab, &tmap_a, bar, (int)(kb * kBK), (int)(mt * kBM), (int)bi);
+                    ptx::tma_load_3d_pair(ab + S::kA, &tmap_b, bar, (int)(kb * kBK), (int)(nt * BN + rank * 128), (int)bi);
+                    ptx::tma_load_4d_pair(sf, &tmap_sfa, bar, 0, (int)kb, (int)mt, (int)bi);
+                    ptx::tma_load_4d_pair(sf + kSfChunk, &tmap_sfb, bar, 0, (int)kb, (int)(nt * 2), (int)bi);
+                    ptx::tma_load_4d_pair(sf + 2 * kSfChunk, &tmap_sfb, bar, 0, (int)kb, (int)(nt * 2 + 1), (int)bi);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (even CTA only) ----------------
+        if (rank == 0 && ptx::elect_one()) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int64_t t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
+                if (tile_i >= 1 && !ptx::mbar_wait(ptx::smem_u32(acc_empty), (tile_i & 1) ^ 1, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full[s]), ph, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem + (size_t)s * S::kAB);
+                    const uint32_t b_addr = a_addr + S::kA;
+                    const uint32_t sf_addr = ptx::smem_u32(smem + S::kSfOff + (size_t)s * S::kSF);
+                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfaCol, ptx::smem_desc(sf_addr, 0, 128, 0));
+                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol, ptx::smem_desc(sf_addr + kSfChunk, 0, 128, 0));
+                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + 4, ptx::smem_desc(sf_addr + 2 * kSfChunk, 0, 128, 0));
+#pragma unroll
+                    for (int k = 0; k < kBK / 32; ++k) {
+                        const uint64_t ad = ptx::smem_desc(a_addr + 32 * k, 0, 1024, 2);
+                        const uint64_t bd = ptx::smem_desc(b_addr + 32 * k, 0, 1024, 2);
+                        const uint32_t id = g.idesc | ((uint32_t)k << 4) | ((uint32_t)k << 29);
+                        ptx::tc_mma_mxf8f6f4_pair(tmem_base, ad, bd, id, (tmem_base + kSfaCol) | ((uint32_t)k << 30),
+                                                  (tmem_base + kSfbCol) | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit_pair(ptx::smem_u32(&empty[s]), 3);      // both CTAs may refill the stage
+                }
+                if (ok) ptx::tc_commit_pair(ptx::smem_u32(acc_full), 3);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs, 128 rows each) ----------------
+        const int e = warp - 2;
+        const int q = warp & 3;
+        const int half = e >> 2;
+        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * 2048);
+        const uint32_t acc_empty_even = ptx::mapa(ptx::smem_u32(acc_empty), 0);
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int64_t t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
+            int64_t bi, mt2, nt;
+            tile_coords(t, g, tiles_per_batch, bi, mt2, nt);
+            if (!ptx::mbar_wait(ptx::smem_u32(acc_full), tile_i & 1, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const int64_t row0 = (2 * mt2 + rank) * kBM + q * 32;
+            const int64_t dest = g.rows_per_dest > 0 ? row0 / g.rows_per_dest : 0;
+            const int64_t row0_dest = row0 - dest * g.rows_per_dest;
+            const CUtensorMap* tmap_c = &tmaps_c.m[dest < kMaxDests ? dest : 0];
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            constexpr int kCols = BN / 2;
+            uint32_t v[kCols];
+#pragma unroll
+            for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(acc_empty_even);
+            if (row0 < g.M) round_and_store<BN>(v, half, lane, stg, g, tmap_c, row0, row0_dest, nt, bi);
+        }
+        if (lane == 0) ptx::bulk_wait_all();
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_arrive();                                    // the partner no longer touches this CTA's memory
+    ptx::cluster_wait();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(g.status, MXQ_ERR_DEVICE);
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -403,6 +594,43 @@ static int make_output_map(CUtensorMap* m, void* base, int64_t batch, int64_t M,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
+}
+
+// E8M0 scales as a 4-D tensor of 512-byte chunks: [batch][128-row chunk][K block][128 words]
+static int make_sf_map(CUtensorMap* m, const void* base, int64_t batch, int64_t rows128, int64_t k_blocks) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MXQ_ERR_CUDA;
+    cuuint64_t dims[4] = {128, (cuuint64_t)k_blocks, (cuuint64_t)rows128, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)kSfChunk, (cuuint64_t)kSfChunk * k_blocks, (cuuint64_t)kSfChunk * k_blocks * rows128};
+    cuuint32_t box[4] = {128, 1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
+}
+
+template <int STAGES>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                            const OutMaps& tc, const GemmArgs& g, cudaStream_t st) {
+    using S = PairSmem<STAGES>;
+    auto kern = gemm_mx_pair_kernel<STAGES>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
+        return MXQ_ERR_CUDA;
+    const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
+    const int pairs = (int)std::min<int64_t>(tiles, sm_count() / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = S::kTotal;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, tc, g) != cudaSuccess) { cudaGetLastError(); return MXQ_ERR_CUDA; }
+    return check_launch();
 }
 
 template <int BN, int STAGES, int ACC_BUFS>
@@ -494,6 +722,24 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     } else if (g.c_tma) {
         rc = make_output_map(&tc.m[0], c, batch, M, N, out_dtype == MXQ_F32);
         if (rc) return rc;
+    }
+    // CTA pairs on 256 x 256 tiles when there is at least one tile per pair of SMs
+    static const int pair_mode = [] { const char* e = getenv("MXQ_GEMM_PAIR"); return e ? atoi(e) : -1; }();
+    const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256) * batch;
+    const bool want_pair = pair_mode == 1 || (pair_mode != 0 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256);
+    if (want_pair && g.c_tma) {
+        GemmArgs gp = g;
+        gp.m_tiles = (M + 255) / 256;
+        gp.n_tiles = (N + 255) / 256;
+        gp.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, 256, 256);
+        CUtensorMap tb2, tsa, tsb;
+        rc = make_operand_map(&tb2, b_codes, batch, N, K, 128);
+        if (rc) return rc;
+        rc = make_sf_map(&tsa, a_scales, batch, g.sfa_rows128, g.k_blocks);
+        if (rc) return rc;
+        rc = make_sf_map(&tsb, b_scales, batch, g.sfb_rows128, g.k_blocks);
+        if (rc) return rc;
+        return launch_gemm_pair<6>(ta, tb2, tsa, tsb, tc, gp, (cudaStream_t)stream);
     }
     if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
     return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
