@@ -726,7 +726,8 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     // CTA pairs on 256 x 256 tiles when there is at least one tile per pair of SMs
     static const int pair_mode = [] { const char* e = getenv("MXQ_GEMM_PAIR"); return e ? atoi(e) : -1; }();
     const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256) * batch;
-    const bool want_pair = pair_mode == 1 || (pair_mode != 0 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256);
+    // MXQ_GEMM_PAIR: 1 = always, 2 = when the problem fills the SM pairs, unset / 0 = never (default until validated)
+    const bool want_pair = pair_mode == 1 || (pair_mode == 2 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256);
     if (want_pair && g.c_tma) {
         GemmArgs gp = g;
         gp.m_tiles = (M + 255) / 256;
