@@ -213,20 +213,28 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* empty = bars + STAGES;             // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;      // [ACC_BUFS]
     uint64_t* acc_empty = acc_full + ACC_BUFS;   // [ACC_BUFS]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+    uint64_t* sf_free = acc_empty + ACC_BUFS;    // [ACC_BUFS]  (kSfSwap only)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_free + ACC_BUFS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr uint32_t kAccCols = BN * ACC_BUFS;
-    constexpr uint32_t kSfaCol = kAccCols;
-    constexpr uint32_t kSfbCol = kAccCols + 4;
     constexpr uint32_t kTmemCols = 512;
-    static_assert(kAccCols + 4 + BN / 32 <= kTmemCols, "tensor memory budget");
+    // Two 256-column accumulators fill tensor memory completely.  The 12 scale columns of the tile
+    // being computed then live in the first columns of the OTHER accumulator buffer: the previous
+    // tile's epilogue hands those columns back (sf_free) as soon as it has read them, long before
+    // it has drained the rest, so the next tile's MMAs start almost at once.
+    constexpr bool kSfSwap = kAccCols + 4 + BN / 32 > kTmemCols;
+    static_assert(!kSfSwap || (ACC_BUFS == 2 && kAccCols == kTmemCols), "scale columns need a home");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
-        for (int b = 0; b < ACC_BUFS; ++b) { ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1); ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpiWarps); }
+        for (int b = 0; b < ACC_BUFS; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpiWarps);
+            ptx::mbar_init(ptx::smem_u32(&sf_free[b]), 4);               // the four warps that own columns 0..31
+        }
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -287,8 +295,12 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int buf = tile_i % ACC_BUFS;
                 const uint32_t acc_ph = (tile_i / ACC_BUFS) & 1;
                 if (tile_i >= (uint32_t)ACC_BUFS && !ptx::mbar_wait(ptx::smem_u32(&acc_empty[buf]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                if (kSfSwap && tile_i >= 1 &&
+                    !ptx::mbar_wait(ptx::smem_u32(&sf_free[buf ^ 1]), ((tile_i - 1) / ACC_BUFS) & 1, abort_flag)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                const uint32_t kSfaCol = kSfSwap ? (uint32_t)(buf ^ 1) * BN : kAccCols;
+                const uint32_t kSfbCol = kSfaCol + 4;
                 for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -353,8 +365,19 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // then overlap the next tile's main loop even with a single accumulator buffer.
             constexpr int kCols = BN / 2;
             uint32_t v[kCols];
+            if (kSfSwap && half == 0) {
+                // columns 0..31 first: the next tile's scales go there
+                ptx::tmem_ld_32x32b_x32(taddr, v);
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sf_free[buf]));
 #pragma unroll
-            for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
+                for (int c = 32; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + c, v + c);
+            } else {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
+            }
             ptx::tmem_ld_wait();
             ptx::tc_fence_before();
             __syncwarp();
@@ -724,10 +747,12 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
         if (rc) return rc;
     }
     // CTA pairs on 256 x 256 tiles when there is at least one tile per pair of SMs
-    static const int pair_mode = [] { const char* e = getenv("MXQ_GEMM_PAIR"); return e ? atoi(e) : -1; }();
+    static const int pair_mode = [] { const char* e = getenv("MXQ_GEMM_PAIR"); return e ? atoi(e) : 2; }();
     const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256) * batch;
-    // MXQ_GEMM_PAIR: 1 = always, 2 = when the problem fills the SM pairs, unset / 0 = never (default until validated)
-    const bool want_pair = pair_mode == 1 || (pair_mode == 2 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256);
+    // MXQ_GEMM_PAIR: 0 = never, 1 = always, 2 (default) = for problems that fill every SM pair and
+    // have a long K loop (measured: +2..5 % there, slower for short K where the epilogue dominates)
+    const bool want_pair = pair_mode == 1 ||
+                           (pair_mode == 2 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256 && K >= 1024);
     if (want_pair && g.c_tma) {
         GemmArgs gp = g;
         gp.m_tiles = (M + 255) / 256;
@@ -742,6 +767,9 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
         if (rc) return rc;
         return launch_gemm_pair<6>(ta, tb2, tsa, tsb, tc, gp, (cudaStream_t)stream);
     }
+    // two 256-column accumulators (scale columns parked in the idle one); MXQ_GEMM_ACC2=0 selects one
+    static const int acc2 = [] { const char* e = getenv("MXQ_GEMM_ACC2"); return e ? atoi(e) : 1; }();
+    if (bn == 256 && acc2) return launch_gemm<256, 4, 2>(ta, tb, tc, g, (cudaStream_t)stream);
     if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
     return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
 }
