@@ -57,12 +57,23 @@ class _PeerSlabs:
     def __init__(self, group, world, rank, rows, cols, device):
         from . import _backend as be
         self.rows, self.cols, self.world, self.device = rows, cols, world, device
+        self.local, self.opened, self.my_slab_on = None, [], []
         slab_bytes = rows * cols * 4
-        self.local, handle = be.peer_alloc(device, world * slab_bytes)
+        handle = None
+        try:
+            self.local, handle = be.peer_alloc(device, world * slab_bytes)
+        except Exception:                                   # every rank still takes part in the exchange below
+            pass
         handles = [None] * world
         dist.all_gather_object(handles, handle, group=group)
-        self.opened = [None if r == rank else be.peer_open(device, h) for r, h in enumerate(handles)]
-        self.my_slab_on = [(self.local if r == rank else p) + rank * slab_bytes for r, p in enumerate(self.opened)]
+        self.ok = all(h is not None for h in handles)
+        if self.ok:
+            try:
+                self.opened = [None if r == rank else be.peer_open(device, h) for r, h in enumerate(handles)]
+                self.my_slab_on = [(self.local if r == rank else p) + rank * slab_bytes
+                                   for r, p in enumerate(self.opened)]
+            except Exception:
+                self.ok = False
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
 
     def close(self):
@@ -106,6 +117,21 @@ class TensorParallelFFN(torch.nn.Module):
         self.w_down = torch.nn.Parameter(torch.empty(hidden, hi - lo, **kw))
         self._packed = None
         self._slabs = None
+        self._no_peer = False
+
+    def _make_slabs(self, rows, device):
+        """Collective: either every rank ends up with mapped receive buffers or none does (then the
+        NCCL reduce-scatter is used from here on)."""
+        slabs = _PeerSlabs(self.group, self.world, self.rank, rows, self.hidden, device)
+        flag = torch.tensor([1.0 if slabs.ok else 0.0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if float(flag.item()) < 1.0:                        # no IPC / peer mapping somewhere: nobody uses it
+            slabs.close()
+            dist.barrier(group=self.group)
+            slabs.free()
+            self._no_peer = True
+            return None
+        return slabs
 
     def release_peer_buffers(self):
         """Unmap and free the receive buffers of the scattering GEMM (all ranks call this together)."""
@@ -204,8 +230,8 @@ class TensorParallelFFN(torch.nn.Module):
             return be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=h.dtype, bfloat_bits=bits,
                               round_mode=out_rnd)[0]
         rows = T // self.world
-        if self._slabs is None and _peer_access_ok(h.device, self.world):
-            self._slabs = _PeerSlabs(self.group, self.world, self.rank, rows, self.hidden, h.device)
+        if self._slabs is None and not self._no_peer and _peer_access_ok(h.device, self.world):
+            self._slabs = self._make_slabs(rows, h.device)
         sl = self._slabs
         if sl is not None and (sl.rows, sl.cols) == (rows, self.hidden):
             # GEMM + scatter in one kernel; the previous call's slabs were consumed before any rank
