@@ -26,7 +26,7 @@ extern "C" int mxq_quantize_mx(const void* in, void* out, void* codes, void* sca
     if (codes && elem_mbits > 8) return MXQ_ERR_UNSUPPORTED;           // no one-byte container
     if (block <= 0 || block > axis_len) block = (int)std::min<int64_t>(axis_len, 0x7fffffff);
     MxArgs a;
-    a.in = in; a.in2 = nullptr; a.out = out; a.codes = (uint8_t*)codes; a.scales = (uint8_t*)scales;
+    a.in = in; a.in2 = nullptr; a.sig_table = nullptr; a.out = out; a.codes = (uint8_t*)codes; a.scales = (uint8_t*)scales;
     a.noise = (const float*)noise;
     a.pre = pre; a.axis_len = axis_len; a.post = post;
     a.block = block;

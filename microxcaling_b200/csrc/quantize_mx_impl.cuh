@@ -45,6 +45,7 @@ struct FastDiv {
 struct MxArgs {
     const void* in;
     const void* in2;        // second input of a fused prologue (SiLU(in) * in2), else unused
+    const uint16_t* sig_table;   // sigmoid chain of every bfloat16 bit pattern (fused prologue only)
     void* out;
     uint8_t* codes;
     uint8_t* scales;
@@ -467,16 +468,21 @@ constexpr int kLastBfUnroll = 4;
 // warp's 32 blocks lie in one row of the GEMM scale layout (4 lanes per block and
 // a multiple of 32 blocks per row), so the scale index is computed once per thread.
 // PRO = 1: the value that is quantized is SiLU(in) * in2, computed per element
-// as the bfloat16 vector chain of the gated feed-forward block (silu_chain, then
-// the product, each step rounded to bfloat16) instead of being loaded: the
-// activation tensor is never written to memory.  Codes and scales only.
-template <int MODE, bool WANT_DQ, int CK, int PRO = 0>
-__global__ void __launch_bounds__(kLastBfThreads)
-mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block, const int row_local) {
-    static_assert(PRO == 0 || (!WANT_DQ && CK != CK_NONE), "the fused prologue produces the packed operand only");
+// as the bfloat16 vector chain of the gated feed-forward block (sigmoid chain,
+// gate * sigmoid, then the product with in2, each step rounded to bfloat16)
+// instead of being loaded: the activation tensor is never written to memory.
+// Codes and scales only.  The sigmoid chain is a pure function of the 16 input
+// bits, so it is read from a 64 Ki-entry table (built once per device by running
+// the chain itself on every bit pattern) held in shared memory; the kernel is
+// then persistent, 1024 threads per SM, one table load per CTA.
+constexpr int kSwigluThreads = 1024;
+
+template <int MODE, bool WANT_DQ, int CK, int PRO>
+__device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_t nvec, const int lanes_per_block,
+                                                   const int row_local, const int64_t tile_base,
+                                                   const uint16_t* sig_tab) {
     const int lane_shift = 31 - __clz(lanes_per_block);
-    const int64_t base = (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll) +
-                         (threadIdx.x >> 5) * (32 * kLastBfUnroll) + (threadIdx.x & 31);
+    const int64_t base = tile_base + (threadIdx.x >> 5) * (32 * kLastBfUnroll) + (threadIdx.x & 31);
     uint4 raw[kLastBfUnroll];
     bool live[kLastBfUnroll];
 #pragma unroll
@@ -495,9 +501,9 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float s0, y0, s1, y1;
-                silu_chain(bf_lo(g[i]), s0, y0);
-                silu_chain(bf_hi(g[i]), s1, y1);
+                const float s0 = __uint_as_float((uint32_t)sig_tab[g[i] & 0xffffu] << 16);
+                const float s1 = __uint_as_float((uint32_t)sig_tab[g[i] >> 16] << 16);
+                const float y0 = rb(bf_lo(g[i]) * s0), y1 = rb(bf_hi(g[i]) * s1);
                 o[i] = pack_bf(rb(y0 * bf_lo(up[i])), rb(y1 * bf_hi(up[i])));
             }
             raw[u] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -553,6 +559,26 @@ mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_
                                      w[2 * i], w[2 * i + 1]);
             reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
         }
+    }
+}
+
+template <int MODE, bool WANT_DQ, int CK, int PRO = 0>
+__global__ void __launch_bounds__(PRO ? kSwigluThreads : kLastBfThreads)
+mx_lastaxis_bf16_kernel(const MxArgs a, const int64_t nvec, const int lanes_per_block, const int row_local) {
+    static_assert(PRO == 0 || (!WANT_DQ && CK != CK_NONE), "the fused prologue produces the packed operand only");
+    if (PRO == 0) {
+        lastaxis_bf16_tile<MODE, WANT_DQ, CK, 0>(a, nvec, lanes_per_block, row_local,
+                                                 (int64_t)blockIdx.x * (kLastBfThreads * kLastBfUnroll), nullptr);
+    } else {
+        extern __shared__ uint4 sig_tab_smem[];
+        const uint4* src = reinterpret_cast<const uint4*>(a.sig_table);
+        for (int i = threadIdx.x; i < 65536 * 2 / 16; i += kSwigluThreads) sig_tab_smem[i] = __ldg(src + i);
+        __syncthreads();
+        const int64_t per_tile = (int64_t)kSwigluThreads * kLastBfUnroll;
+        const int64_t ntiles = (nvec + per_tile - 1) / per_tile;
+        for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x)
+            lastaxis_bf16_tile<MODE, WANT_DQ, CK, PRO>(a, nvec, lanes_per_block, row_local, t * per_tile,
+                                                       reinterpret_cast<const uint16_t*>(sig_tab_smem));
     }
 }
 

@@ -13,12 +13,19 @@
 namespace mxq {
 template <int MODE>
 static int launch_swiglu(const MxArgs& a, int64_t nvec, cudaStream_t st) {
-    const int64_t tile = (int64_t)kLastBfThreads * kLastBfUnroll;
-    const int64_t grid = (nvec + tile - 1) / tile;
-    if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+    const int64_t tile = (int64_t)kSwigluThreads * kLastBfUnroll;
+    const int64_t ntiles = (nvec + tile - 1) / tile;
+    const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sm_count());       // persistent: one CTA per SM
     const int rl = a.sf_gemm && a.nblk % 32 == 0;
-    if (a.fmt.ebits == 5) mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2, 1><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, 4, rl);
-    else mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3, 1><<<(unsigned)grid, kLastBfThreads, 0, st>>>(a, nvec, 4, rl);
+    constexpr int kTabBytes = 65536 * 2;
+    auto k5 = mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2, 1>;
+    auto k4 = mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3, 1>;
+    auto kern = a.fmt.ebits == 5 ? k5 : k4;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTabBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return MXQ_ERR_CUDA;
+    }
+    kern<<<grid, kSwigluThreads, kTabBytes, st>>>(a, nvec, 4, rl);
     return check_launch();
 }
 }  // namespace mxq
@@ -38,6 +45,8 @@ extern "C" int mxq_swiglu_quantize_mx(const void* gate, const void* up, void* co
     if (!aligned16(gate) || !aligned16(up) || !aligned8(codes)) return MXQ_ERR_ALIGN;
     if (rows * (K / 32) > 0xffffffffLL) return MXQ_ERR_TOO_LARGE;
     MxArgs a;
+    a.sig_table = sigmoid_table();
+    if (!a.sig_table) return MXQ_ERR_CUDA;
     a.in = gate; a.in2 = up; a.out = nullptr; a.codes = (uint8_t*)codes; a.scales = (uint8_t*)scales; a.noise = nullptr;
     a.pre = rows; a.axis_len = K; a.post = 1;
     a.block = 32;

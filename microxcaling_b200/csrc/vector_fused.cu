@@ -18,6 +18,28 @@
 
 namespace mxq {
 
+__global__ void build_sigmoid_table_kernel(uint16_t* tab) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) return;
+    float s, y;
+    silu_chain(__uint_as_float(i << 16), s, y);
+    tab[i] = (uint16_t)(__float_as_uint(s) >> 16);
+}
+
+const uint16_t* sigmoid_table() {
+    static uint16_t* tabs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!tabs[dev]) {
+        uint16_t* t = nullptr;
+        if (cudaMalloc(&t, 65536 * sizeof(uint16_t)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        build_sigmoid_table_kernel<<<65536 / 256, 256>>>(t);
+        if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(0) != cudaSuccess) { cudaFree(t); return nullptr; }
+        tabs[dev] = t;
+    }
+    return tabs[dev];
+}
+
 constexpr int kVecThreads = 256;
 
 template <bool HAS_UP, bool WANT_SIG>
@@ -54,6 +76,54 @@ silu_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, u
         reinterpret_cast<uint16_t*>(out)[t] = (uint16_t)(__float_as_uint(y) >> 16);
         if (WANT_SIG) reinterpret_cast<uint16_t*>(sig)[t] = (uint16_t)(__float_as_uint(s) >> 16);
     }
+}
+
+// The same chain for large tensors: the sigmoid part is a pure function of the 16 input bits
+// and is read from the table of sigmoid_table() held in shared memory (persistent CTAs, one
+// table load each); the multiplications and their roundings are done as above.
+constexpr int kTabThreads = 1024;
+constexpr int kTabBytes = 65536 * 2;
+
+template <bool HAS_UP, bool WANT_SIG>
+__global__ void __launch_bounds__(kTabThreads)
+silu_tab_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
+                     uint4* __restrict__ sig, const uint16_t* __restrict__ table, const int64_t nvec) {
+    extern __shared__ uint4 tab_smem[];
+    for (int i = threadIdx.x; i < kTabBytes / 16; i += kTabThreads) tab_smem[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+    __syncthreads();
+    const uint16_t* tab = reinterpret_cast<const uint16_t*>(tab_smem);
+    const int64_t stride = (int64_t)gridDim.x * kTabThreads;
+    for (int64_t v = (int64_t)blockIdx.x * kTabThreads + threadIdx.x; v < nvec; v += stride) {
+        const uint4 g4 = __ldg(gate + v);
+        uint4 u4 = make_uint4(0, 0, 0, 0);
+        if (HAS_UP) u4 = __ldg(up + v);
+        const uint32_t g[4] = {g4.x, g4.y, g4.z, g4.w};
+        const uint32_t u[4] = {u4.x, u4.y, u4.z, u4.w};
+        uint32_t o[4], sg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t b0 = tab[g[i] & 0xffffu], b1 = tab[g[i] >> 16];
+            float y0 = rb(bf_lo(g[i]) * __uint_as_float(b0 << 16)), y1 = rb(bf_hi(g[i]) * __uint_as_float(b1 << 16));
+            if (HAS_UP) { y0 = rb(y0 * bf_lo(u[i])); y1 = rb(y1 * bf_hi(u[i])); }
+            o[i] = pack_bf(y0, y1);
+            sg[i] = b0 | (b1 << 16);
+        }
+        out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (WANT_SIG) sig[v] = make_uint4(sg[0], sg[1], sg[2], sg[3]);
+    }
+}
+
+template <bool HAS_UP, bool WANT_SIG>
+static int launch_silu_tab(const uint4* g, const uint4* u, uint4* o, uint4* s, const uint16_t* table, int64_t nvec,
+                           cudaStream_t st) {
+    auto kern = silu_tab_bf16_kernel<HAS_UP, WANT_SIG>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTabBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return MXQ_ERR_CUDA;
+    }
+    const unsigned grid = (unsigned)std::min<int64_t>((nvec + kTabThreads - 1) / kTabThreads, sm_count());
+    kern<<<grid, kTabThreads, kTabBytes, st>>>(g, u, o, s, table, nvec);
+    return check_launch();
 }
 
 // RMSNorm of one row per CTA (mx/layernorm.py:113-125):
@@ -221,6 +291,16 @@ extern "C" int mxq_silu_bf16(const void* gate, const void* up, void* out, void* 
     cudaStream_t st = (cudaStream_t)stream;
     const uint4 *g = (const uint4*)gate, *u = (const uint4*)up;
     uint4 *o = (uint4*)out, *s = (uint4*)sig;
+    if (n % 8 == 0 && n >= (int64_t)1 << 22) {
+        // large tensors: table-driven kernel (one 128 KB table load per SM pays off)
+        const uint16_t* table = sigmoid_table();
+        if (table) {
+            if (up && sig) return launch_silu_tab<true, true>(g, u, o, s, table, nvec, st);
+            if (up) return launch_silu_tab<true, false>(g, u, o, s, table, nvec, st);
+            if (sig) return launch_silu_tab<false, true>(g, u, o, s, table, nvec, st);
+            return launch_silu_tab<false, false>(g, u, o, s, table, nvec, st);
+        }
+    }
     if (up && sig) silu_bf16_kernel<true, true><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
     else if (up) silu_bf16_kernel<true, false><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);
     else if (sig) silu_bf16_kernel<false, true><<<grid, kVecThreads, 0, st>>>(g, u, o, s, nvec, n);

@@ -25,4 +25,8 @@ __device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
     y = rb(q * s);
 }
 
+// Device table of the sigmoid chain for every bfloat16 bit pattern (64 Ki entries of 2 bytes), built on
+// first use on the current device by running silu_chain on each pattern; nullptr on failure.
+const uint16_t* sigmoid_table();
+
 }  // namespace mxq

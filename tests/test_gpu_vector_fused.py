@@ -59,6 +59,23 @@ def test_silu_every_pattern(monkeypatch, n):
     assert same(got, want)
 
 
+def test_silu_large_tensor_uses_the_table_and_matches(monkeypatch):
+    """>= 4 Mi elements take the table-driven kernel: same bits as the composed chain, every pattern included."""
+    torch.manual_seed(9)
+    x = torch.cat([all_bf16_patterns(), (torch.randn((1 << 22) + 4096, device="cuda") * 3).to(torch.bfloat16)])
+    x = x[: (x.numel() // 8) * 8].contiguous()
+    up = (torch.randn(x.numel(), device="cuda") * 2).to(torch.bfloat16)
+    from microxcaling_b200 import _backend
+    got, sig = _backend.silu_bf16(x, None, want_sig=True)
+    want = composed(monkeypatch, lambda: mx.silu(x, mx_specs=SP))
+    assert same(got, want)
+    got2 = _backend.silu_bf16(x, up)
+    want2 = composed(monkeypatch, lambda: mx.simd_mul(mx.silu(x, mx_specs=SP), up, mx_specs=SP))
+    assert same(got2, want2)
+    small_sig = _backend.silu_bf16(x[:4096].contiguous(), None, want_sig=True)[1]
+    assert same(sig[:4096], small_sig)
+
+
 def test_silu_backward_uses_saved_sigmoid(monkeypatch):
     torch.manual_seed(0)
     x = (torch.randn(300, 257, device="cuda") * 4).to(torch.bfloat16)
