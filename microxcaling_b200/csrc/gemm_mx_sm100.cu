@@ -10,17 +10,19 @@
 // applies the bfloat rounding of mx_specs (and the bias add with its second
 // rounding, mx/linear.py:88-96) while the accumulator is read out.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer: A and B tiles (128-byte swizzle) and the scale
 //               chunks into a STAGES-deep shared-memory ring
 //   warp 1      MMA issuer: copies the scales to tensor memory (tcgen05.cp),
 //               issues four K=32 MMAs per 128-wide K block, commits the stage
 //               back to the producer and finished accumulators to the epilogue
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one 32-lane quarter
-//               each), rounding, stores
+//   warps 2..9  epilogue: two warps per 32-lane quarter of tensor memory read
+//               half of the accumulator columns each (tcgen05.ld), round, and
+//               store through a swizzled staging tile with TMA
 // Accumulators are double buffered in tensor memory so the epilogue of one
-// tile overlaps the main loop of the next.  All waits are bounded; on time-out
-// the kernel records a status word, drains and exits.
+// tile overlaps the main loop of the next; a second kernel runs CTA pairs
+// (cta_group::2) on 256 x 256 tiles.  All waits are bounded; on time-out the
+// kernel records a status word, drains and exits.
 #include <cuda.h>
 #include <algorithm>
 #include <cstring>
