@@ -19,8 +19,9 @@ its FFN admits without changing results beyond fp32 accumulation order:
     128-row tile is stored straight into the receive buffer of the rank that
     owns those tokens (mxq_gemm_mx_scatter), one small NCCL all-reduce orders
     the ranks, and each rank adds the slabs it received in rank order
-    (mxq_sum_slabs_f32).  MXQ_TP_FUSED_SCATTER=0 selects the NCCL
-    reduce-scatter instead.
+    (mxq_sum_slabs_f32).  This is the default for two ranks; for more ranks the
+    NCCL reduce-scatter is faster (see _peer_access_ok) and is used unless
+    MXQ_TP_FUSED_SCATTER=1.
 
 On CUDA tensors the GEMMs run on packed operands through libmxq; on CPU tensors
 (used by the gloo tests of this logic) the same steps run on fake-quantized
@@ -93,7 +94,12 @@ class _PeerSlabs:
 
 
 def _peer_access_ok(device, world):
-    if os.environ.get("MXQ_TP_FUSED_SCATTER", "1") == "0" or world > 8:
+    # Measured on B200 / NVSwitch (config-5 FFN forward): 2 GPUs 5.36 ms with the scattering GEMM vs 5.84 ms
+    # with the NCCL reduce-scatter; 8 GPUs 3.20 ms vs 2.28 ms -- with seven of eight tiles leaving over NVLink
+    # as 64-byte row segments the links are used at well under half their rate, so the scattering GEMM is the
+    # default only for two ranks.  MXQ_TP_FUSED_SCATTER=1 forces it, =0 forbids it.
+    mode = os.environ.get("MXQ_TP_FUSED_SCATTER", "")
+    if mode == "0" or world > 8 or (mode != "1" and world > 2):
         return False
     me = device.index if device.index is not None else torch.cuda.current_device()
     n = torch.cuda.device_count()
