@@ -189,3 +189,34 @@ def test_sum_slabs_adds_in_order(be):
     for k in range(1, 5):
         want = want + s[k]
     assert torch.equal(be.sum_slabs(s.contiguous()), want)
+
+
+def _sampled_gemm_check(be, M, N, K, fa, fb, n_rows=24, n_cols=512, seed=0):
+    """Full-size GEMM (whatever tile engine the library picks for it) checked on a random sample of output
+    rows x columns against the double-accumulated product of the dequantized operands."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    A = (torch.randn(M, K, generator=g, device="cuda") * 1.5).to(torch.bfloat16)
+    B = (torch.randn(N, K, generator=g, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    dqa, ca, sa, ka = quant_operand(be, A, fa, M)
+    dqb, cb, sb, kb = quant_operand(be, B, fb, N)
+    C = be.gemm_mx(ca, sa, cb, sb, 1, M, N, K, ka, kb, torch.float32, 0, -1)[0]
+    torch.cuda.synchronize()
+    assert be.device_status() == 0
+    rs = np.random.default_rng(seed)
+    rows = np.sort(rs.choice(M, n_rows, replace=False))
+    cols = np.sort(rs.choice(N, n_cols, replace=False))
+    a = dqa[torch.as_tensor(rows, device="cuda")].float().cpu().numpy()[None]
+    b = dqb[torch.as_tensor(cols, device="cuda")].float().cpu().numpy()[None]
+    ref, refabs = oracle.gemm_nt(a, b, want_abs=True)
+    got = C[torch.as_tensor(rows, device="cuda")][:, torch.as_tensor(cols, device="cuda")].cpu().numpy().astype(np.float64)
+    assert np.all(np.abs(got - ref[0]) <= 2.0 ** -22 * refabs[0] + 1e-30)
+
+
+def test_config3_gemm_full_size_sampled(be):
+    """Config 3: 8192 tokens x 4096 -> 4096, MXFP8 operands (forward product)."""
+    _sampled_gemm_check(be, 8192, 4096, 4096, "fp8_e4m3", "fp8_e4m3")
+
+
+def test_config5_gemm_full_size_sampled(be):
+    """Config 5 gate/up projection: 16384 tokens x 8192 -> 28672, fp8_e4m3 activations x fp4_e2m1 weights."""
+    _sampled_gemm_check(be, 16384, 28672, 8192, "fp8_e4m3", "fp4_e2m1", n_rows=16, n_cols=384, seed=1)
