@@ -140,10 +140,28 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
     __shared__ float part[kNormThreads / 32];
     __shared__ float r_shared;
     const bool vec = (hidden & 7) == 0;
+    // rows of up to kNormKeep * 256 vectors stay in registers between the two passes (one read of x)
+    constexpr int kNormKeep = 4;
+    const bool keep = vec && hidden / 8 <= (int64_t)kNormKeep * kNormThreads;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint16_t* xr = x + row * hidden;
         float acc = 0.f;
-        if (vec) {
+        uint4 kept[kNormKeep];
+        if (keep) {
+            const uint4* xv = reinterpret_cast<const uint4*>(xr);
+#pragma unroll
+            for (int k = 0; k < kNormKeep; ++k) {
+                const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
+                kept[k] = i < hidden / 8 ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
+                const uint32_t q[4] = {kept[k].x, kept[k].y, kept[k].z, kept[k].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = bf_lo(q[j]), hi = bf_hi(q[j]);
+                    acc += rb(lo * lo);
+                    acc += rb(hi * hi);
+                }
+            }
+        } else if (vec) {
             const uint4* xv = reinterpret_cast<const uint4*>(xr);
             for (int64_t i = threadIdx.x; i < hidden / 8; i += kNormThreads) {
                 const uint4 v = __ldg(xv + i);
@@ -185,8 +203,13 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
             const uint4* xv = reinterpret_cast<const uint4*>(xr);
             const uint4* wv = reinterpret_cast<const uint4*>(w);
             const uint4* bv = reinterpret_cast<const uint4*>(b);
-            for (int64_t i = threadIdx.x; i < hidden / 8; i += kNormThreads) {
-                const uint4 v = __ldg(xv + i), ww = __ldg(wv + i);
+            const int64_t nv = hidden / 8;
+#pragma unroll 1
+            for (int64_t i = threadIdx.x, k = 0; i < nv; i += kNormThreads, ++k) {
+                uint4 v;
+                if (keep) v = k == 0 ? kept[0] : k == 1 ? kept[1] : k == 2 ? kept[2] : kept[3];
+                else v = __ldg(xv + i);
+                const uint4 ww = __ldg(wv + i);
                 uint4 bb = make_uint4(0, 0, 0, 0);
                 if (b) bb = __ldg(bv + i);
                 const uint32_t q[4] = {v.x, v.y, v.z, v.w}, wq[4] = {ww.x, ww.y, ww.z, ww.w}, bq[4] = {bb.x, bb.y, bb.z, bb.w};
