@@ -246,11 +246,33 @@ class TensorParallelFFN(torch.nn.Module):
             dist.all_reduce(sl.token, group=self.group)           # every rank's tiles have landed
             out = be.sum_slabs(sl.local, self.world, (rows, self.hidden), h.device)
         else:
-            part = be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=torch.float32, bfloat_bits=0,
-                              round_mode=-1)[0]
-            out = self._reduce_scatter_rows(part)
+            out = self._down_chunked(ac, as_, ak, dc, ds, dk, T, Il, rows)
         out = quantize_elemwise_op(out, sp, round=sp["round_output"])
         return out.to(h.dtype)
+
+    def _down_chunked(self, ac, as_, ak, dc, ds, dk, T, Il, rows):
+        """Down projection + NCCL reduce-scatter, pipelined: the output features are cut into slabs (whole
+        128-row groups of the packed weight, so codes and scale chunks of a slab are contiguous); the
+        reduce-scatter of slab c runs on NCCL's stream while the GEMM of slab c + 1 runs on the compute
+        stream.  Every output element still sums the same per-rank partials."""
+        from . import _backend as be
+        H = self.hidden
+        n_slabs = 4 if H % (4 * 256) == 0 else 1
+        slab = H // n_slabs
+        kchunks = (Il + 127) // 128
+        codes2d = dc.reshape(H, Il)
+        outs, works = [], []
+        for c in range(n_slabs):
+            b_codes = codes2d[c * slab:(c + 1) * slab]
+            b_scales = ds.view(-1)[(c * slab // 128) * kchunks * 512:((c + 1) * slab // 128) * kchunks * 512]
+            part = be.gemm_mx(ac, as_, b_codes, b_scales, 1, T, slab, Il, ak, dk, out_dtype=torch.float32,
+                              bfloat_bits=0, round_mode=-1)[0]
+            o = torch.empty((rows, slab), dtype=torch.float32, device=part.device)
+            works.append(dist.reduce_scatter_tensor(o, part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            outs.append(o)
+        for w in works:
+            w.wait()
+        return outs[0] if n_slabs == 1 else torch.cat(outs, dim=1)
 
     def _forward_values(self, h):
         sp = self.mx_specs
