@@ -206,7 +206,9 @@ int mxq_swiglu_quantize_mx(const void* gate, const void* up, void* codes, void* 
  *             'bfloat' and 'round_output'); 0 or 32 bits, or round -1: none
  *   bias      fp32 [N] or NULL: c = round(round(acc) + bias)
  *   tile_n    0 (automatic), 128 or 256
- * K must be a multiple of 128; pointers 16-byte aligned.  The first call on a
+ * K must be a multiple of 32 (when it is not a multiple of 128, the scale bytes of
+ * the missing blocks of the last 128-wide group must be zero, as mxq_quantize_mx
+ * leaves them in a zero-initialised buffer); pointers 16-byte aligned.  The first call on a
  * device allocates a 4-byte status word with cudaMalloc (kept until exit); a
  * kernel that gives up on a wait stores MXQ_ERR_DEVICE there, see
  * mxq_device_status.

@@ -5,7 +5,7 @@ its contraction axis and the result rounded to the vector format of mx_specs.
 On CUDA tensors with FP element formats and block size 32 it runs as
 quantize-to-packed-operand kernels plus the tcgen05 block-scaled GEMM; every
 other case (CPU tensors, fixed-point formats, odd block sizes, contraction
-length not a multiple of 128) follows the reference's construction: fake-quantize
+length not a multiple of 32) follows the reference's construction: fake-quantize
 both operands, multiply with torch, round the result
 (mx/linear.py:62-96, mx/matmul.py:68-96, mx/bmm.py:40-62).
 """
@@ -32,7 +32,7 @@ def _fast_ok(in1, in2, f1, f2, specs, K, r1, r2, out_round):
         return False
     if in1.dtype != in2.dtype or in1.dtype not in (torch.bfloat16, torch.float32, torch.float16):
         return False
-    if specs["block_size"] != 32 or K % 128 != 0 or specs["shared_exp_method"] != "max":
+    if specs["block_size"] != 32 or K % 32 != 0 or specs["shared_exp_method"] != "max":
         return False
     if specs["fp"] > 0 or (0 < specs["bfloat"] < 10):
         return False

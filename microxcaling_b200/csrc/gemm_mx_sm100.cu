@@ -696,7 +696,9 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     if (batch < 0 || M < 0 || N < 0 || K < 0) return MXQ_ERR_BAD_ARG;
     if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
     if (!a_codes || !a_scales || !b_codes || !b_scales || !c) return MXQ_ERR_BAD_ARG;
-    if (K == 0 || K % kBK != 0) return MXQ_ERR_UNSUPPORTED;            // K must be a multiple of 128
+    // K: whole 32-element blocks and a 16-byte row pitch.  A last K block shorter than 128 is zero-filled
+    // by the tiled loads; its unused scale bytes must be finite (the quantizer's buffers are zeroed there).
+    if (K == 0 || K % 32 != 0) return MXQ_ERR_UNSUPPORTED;
     if (a_fmt < 0 || a_fmt > 1 || b_fmt < 0 || b_fmt > 1) return MXQ_ERR_BAD_ARG;
     if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_BAD_ARG;
     if (out_round < -1 || out_round > MXQ_ROUND_EVEN) return MXQ_ERR_BAD_ARG;
@@ -713,7 +715,7 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     g.status = status_word;
     if (!g.status) return MXQ_ERR_CUDA;
     g.M = M; g.N = N; g.K = K; g.batch = batch;
-    g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = K / kBK;
+    g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = (K + kBK - 1) / kBK;
     g.sfa_rows128 = (M + 127) / 128; g.sfb_rows128 = (N + 127) / 128;
     g.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, kBM, bn);
     g.out_dtype = out_dtype;

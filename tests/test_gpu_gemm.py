@@ -57,6 +57,16 @@ def test_gemm_raw_accumulator(be, shape, tile_n):
     assert np.all(np.abs(got - ref) <= 2.0 ** -22 * refabs + 1e-30)
 
 
+@pytest.mark.parametrize("K", [32, 96, 160, 416, 1056])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_contraction_not_multiple_of_128(be, K, tile_n):
+    """K only has to be whole 32-element blocks: the last, short K group is zero-filled by the tiled loads."""
+    got, ref, refabs, _ = run_case(be, 1, 384, 256, K, "fp8_e4m3", "fp6_e3m2", tile_n, seed=K)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -22 * refabs + 1e-30)
+    got, ref, refabs, _ = run_case(be, 2, 200, 136, K, "fp8_e5m2", "fp4_e2m1", 0, seed=K + 1)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -22 * refabs + 1e-30)
+
+
 @pytest.mark.parametrize("fa,fb", [("fp8_e4m3", "fp8_e5m2"), ("fp8_e5m2", "fp8_e5m2"), ("fp8_e4m3", "fp4_e2m1"),
                                    ("fp6_e3m2", "fp6_e3m2"), ("fp6_e2m3", "fp4_e2m1"), ("fp4_e2m1", "fp4_e2m1")])
 def test_gemm_format_pairs(be, fa, fb):
@@ -110,7 +120,7 @@ def test_gemm_nan_block_and_zero_rows(be):
 def test_gemm_rejects_bad_arguments(be):
     z = torch.zeros(128 * 128, dtype=torch.uint8, device="cuda")
     with pytest.raises(be.MxqError):
-        be.gemm_mx(z, z, z, z, 1, 128, 128, 96)           # K not a multiple of 128
+        be.gemm_mx(z, z, z, z, 1, 128, 128, 80)           # K not a multiple of 32
     with pytest.raises(be.MxqError):
         be.gemm_mx(z, z, z, z, 1, 128, 128, 128, a_fmt=3)
 

@@ -156,3 +156,23 @@ def test_packed_weight_is_reused_only_while_unchanged(monkeypatch):
     n3 = len(calls)
     lin(x)                                          # autograd on: no reuse
     assert len(calls) - n3 == 2
+
+
+def test_linear_with_odd_feature_count_takes_the_tensor_core_path(monkeypatch):
+    """in_features = 96 (whole 32-blocks, not a multiple of 128): packed GEMM, same result as the
+    reference construction (fake-quantized operands, torch GEMM, rounding) up to accumulation order."""
+    from microxcaling_b200 import _backend, _mxgemm
+    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16})
+    torch.manual_seed(0)
+    lin = mx.Linear(96, 160, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
+    x = torch.randn(200, 96, device="cuda", dtype=torch.bfloat16)
+    calls = []
+    real = _backend.gemm_mx
+    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    with torch.no_grad():
+        got = lin(x)
+    assert calls
+    monkeypatch.setattr(_mxgemm, "_fast_ok", lambda *a, **k: False)
+    with torch.no_grad():
+        want = lin(x)
+    close_bf16(got, want.float().cpu().numpy(), "linear K=96")
