@@ -107,7 +107,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one mx_strided_bf16_kernel launch on this workload
 # (profiles/mx_strided_bf16_kernel__c2_sweep.md)
-STRIDED_TRAFFIC_BYTES = 223_612_672
+STRIDED_TRAFFIC_BYTES = 216_604_672
 
 
 def mx_linear_block(torch, be, dev):
