@@ -503,8 +503,8 @@ __device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_
             for (int i = 0; i < 4; ++i) {
                 const float s0 = __uint_as_float((uint32_t)sig_tab[g[i] & 0xffffu] << 16);
                 const float s1 = __uint_as_float((uint32_t)sig_tab[g[i] >> 16] << 16);
-                const float y0 = rb(bf_lo(g[i]) * s0), y1 = rb(bf_hi(g[i]) * s1);
-                o[i] = pack_bf(rb(y0 * bf_lo(up[i])), rb(y1 * bf_hi(up[i])));
+                const uint32_t y = rb2(bf_lo(g[i]) * s0, bf_hi(g[i]) * s1);          // gate * sigmoid, rounded
+                o[i] = rb2(bf_lo(y) * bf_lo(up[i]), bf_hi(y) * bf_hi(up[i]));        // ... * up, rounded
             }
             raw[u] = make_uint4(o[0], o[1], o[2], o[3]);
         }

@@ -103,9 +103,9 @@ silu_tab_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ u
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t b0 = tab[g[i] & 0xffffu], b1 = tab[g[i] >> 16];
-            float y0 = rb(bf_lo(g[i]) * __uint_as_float(b0 << 16)), y1 = rb(bf_hi(g[i]) * __uint_as_float(b1 << 16));
-            if (HAS_UP) { y0 = rb(y0 * bf_lo(u[i])); y1 = rb(y1 * bf_hi(u[i])); }
-            o[i] = pack_bf(y0, y1);
+            uint32_t y = rb2(bf_lo(g[i]) * __uint_as_float(b0 << 16), bf_hi(g[i]) * __uint_as_float(b1 << 16));
+            if (HAS_UP) y = rb2(bf_lo(y) * bf_lo(u[i]), bf_hi(y) * bf_hi(u[i]));
+            o[i] = y;
             sg[i] = b0 | (b1 << 16);
         }
         out[v] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -157,8 +157,9 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float lo = bf_lo(q[j]), hi = bf_hi(q[j]);
-                    acc += rb(lo * lo);
-                    acc += rb(hi * hi);
+                    const uint32_t sq = rb2(lo * lo, hi * hi);
+                    acc += bf_lo(sq);
+                    acc += bf_hi(sq);
                 }
             }
         } else if (vec) {
@@ -169,8 +170,9 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float lo = bf_lo(q[k]), hi = bf_hi(q[k]);
-                    acc += rb(lo * lo);
-                    acc += rb(hi * hi);
+                    const uint32_t sq = rb2(lo * lo, hi * hi);
+                    acc += bf_lo(sq);
+                    acc += bf_hi(sq);
                 }
             }
         } else {
@@ -216,11 +218,11 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
                 uint32_t o[4], nn[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float n0 = rb(bf_lo(q[k]) * ri), n1 = rb(bf_hi(q[k]) * ri);
-                    float y0 = rb(bf_lo(wq[k]) * n0), y1 = rb(bf_hi(wq[k]) * n1);
-                    if (b) { y0 = rb(y0 + bf_lo(bq[k])); y1 = rb(y1 + bf_hi(bq[k])); }
-                    o[k] = pack_bf(y0, y1);
-                    nn[k] = pack_bf(n0, n1);
+                    const uint32_t n2 = rb2(bf_lo(q[k]) * ri, bf_hi(q[k]) * ri);
+                    uint32_t y2 = rb2(bf_lo(wq[k]) * bf_lo(n2), bf_hi(wq[k]) * bf_hi(n2));
+                    if (b) y2 = rb2(bf_lo(y2) + bf_lo(bq[k]), bf_hi(y2) + bf_hi(bq[k]));
+                    o[k] = y2;
+                    nn[k] = n2;
                 }
                 reinterpret_cast<uint4*>(orow)[i] = make_uint4(o[0], o[1], o[2], o[3]);
                 if (nrow) reinterpret_cast<uint4*>(nrow)[i] = make_uint4(nn[0], nn[1], nn[2], nn[3]);
@@ -275,11 +277,12 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
             if (lane + 32 * k < nchunk) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float d0 = rb(bf_lo(w[k][i]) - m), d1 = rb(bf_hi(w[k][i]) - m);
-                    const float e0 = rb(EXP2 ? exp2f(d0) : expf(d0)), e1 = rb(EXP2 ? exp2f(d1) : expf(d1));
-                    acc += e0;
-                    acc += e1;
-                    w[k][i] = pack_bf(e0, e1);
+                    const uint32_t d2 = rb2(bf_lo(w[k][i]) - m, bf_hi(w[k][i]) - m);
+                    const float d0 = bf_lo(d2), d1 = bf_hi(d2);
+                    const uint32_t e2 = rb2(EXP2 ? exp2f(d0) : expf(d0), EXP2 ? exp2f(d1) : expf(d1));
+                    acc += bf_lo(e2);
+                    acc += bf_hi(e2);
+                    w[k][i] = e2;
                 }
             }
         }
@@ -293,7 +296,7 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
             if (c < nchunk) {
                 uint32_t o[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[i] = pack_bf(rb(__fdiv_rn(bf_lo(w[k][i]), sum)), rb(__fdiv_rn(bf_hi(w[k][i]), sum)));
+                for (int i = 0; i < 4; ++i) o[i] = rb2(__fdiv_rn(bf_lo(w[k][i]), sum), __fdiv_rn(bf_hi(w[k][i]), sum));
                 orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }

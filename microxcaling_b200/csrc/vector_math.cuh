@@ -16,6 +16,12 @@ __device__ __forceinline__ uint32_t pack_bf(float lo, float hi) {
     return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);   // both already on the bf16 grid
 }
 
+// two fp32 values -> packed pair of nearest-even bfloat16 (lo in bits 0..15): one conversion instruction
+__device__ __forceinline__ uint32_t rb2(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // sigmoid and SiLU of one bfloat16 value q with every intermediate rounded to
 // bfloat16: e = exp(-q), a = e + 1, s = 1 / a, y = q * s  (mx/activations.py:428-434)
 __device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
