@@ -18,27 +18,35 @@
 
 namespace mxq {
 
-__global__ void build_sigmoid_table_kernel(uint16_t* tab) {
+// Tables over all 65536 bfloat16 bit patterns, built on first use by the very operations they replace:
+// WHICH = 0: the sigmoid chain of silu_chain; WHICH = 1: exp rounded to bfloat16 (the softmax numerator).
+template <int WHICH>
+__global__ void build_table_kernel(uint16_t* tab) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 65536u) return;
+    const float q = __uint_as_float(i << 16);
     float s, y;
-    silu_chain(__uint_as_float(i << 16), s, y);
+    if (WHICH == 0) silu_chain(q, s, y);
+    else s = rb(expf(q));
     tab[i] = (uint16_t)(__float_as_uint(s) >> 16);
 }
 
-const uint16_t* sigmoid_table() {
+template <int WHICH>
+static const uint16_t* bf16_table() {
     static uint16_t* tabs[64] = {nullptr};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!tabs[dev]) {
         uint16_t* t = nullptr;
         if (cudaMalloc(&t, 65536 * sizeof(uint16_t)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        build_sigmoid_table_kernel<<<65536 / 256, 256>>>(t);
+        build_table_kernel<WHICH><<<65536 / 256, 256>>>(t);
         if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(0) != cudaSuccess) { cudaFree(t); return nullptr; }
         tabs[dev] = t;
     }
     return tabs[dev];
 }
+
+const uint16_t* sigmoid_table() { return bf16_table<0>(); }
 
 constexpr int kVecThreads = 256;
 
@@ -249,13 +257,26 @@ constexpr int kSmMaxVec = 8;
 
 __device__ __forceinline__ float nan_max(float a, float b) { return (b > a || b != b) ? b : a; }   // NaN wins, like torch.max
 
-template <bool EXP2>
-__global__ void __launch_bounds__(kSmThreads)
-softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const int64_t rows, const int cols) {
+// TAB: exp(d) of the bfloat16 value d comes from the 64 Ki-entry table (shared memory, persistent
+// 1024-thread CTAs).  The division e / s is done as e * (1/s) with 1/s correctly rounded: e and s have 8
+// significant bits each, so e / s is never a bfloat16 rounding midpoint and stays at least 2^-17 (relative)
+// away from one, far more than the 2^-23 error of the product, hence the bfloat16 result is the one of the
+// exact division; quotients that would round in bfloat16's subnormal range take the exact division.
+template <bool EXP2, bool TAB>
+__global__ void __launch_bounds__(TAB ? kTabThreads : kSmThreads)
+softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const uint16_t* __restrict__ table,
+                    const int64_t rows, const int cols) {
+    extern __shared__ uint4 exp_tab_smem[];
+    constexpr int kThreads = TAB ? kTabThreads : kSmThreads;
+    if (TAB) {
+        for (int i = threadIdx.x; i < kTabBytes / 16; i += kThreads) exp_tab_smem[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+        __syncthreads();
+    }
+    const uint16_t* tab = reinterpret_cast<const uint16_t*>(exp_tab_smem);
     const int lane = threadIdx.x & 31;
     const int nchunk = cols >> 3;
-    const int64_t warps = (int64_t)gridDim.x * (kSmThreads / 32);
-    for (int64_t row = (int64_t)blockIdx.x * (kSmThreads / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t row = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
         const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
         uint32_t w[kSmMaxVec][4];
         float m = -CUDART_INF_F;
@@ -278,8 +299,13 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t d2 = rb2(bf_lo(w[k][i]) - m, bf_hi(w[k][i]) - m);
-                    const float d0 = bf_lo(d2), d1 = bf_hi(d2);
-                    const uint32_t e2 = rb2(EXP2 ? exp2f(d0) : expf(d0), EXP2 ? exp2f(d1) : expf(d1));
+                    uint32_t e2;
+                    if (TAB) {
+                        e2 = (uint32_t)tab[d2 & 0xffffu] | ((uint32_t)tab[d2 >> 16] << 16);
+                    } else {
+                        const float d0 = bf_lo(d2), d1 = bf_hi(d2);
+                        e2 = rb2(EXP2 ? exp2f(d0) : expf(d0), EXP2 ? exp2f(d1) : expf(d1));
+                    }
                     acc += bf_lo(e2);
                     acc += bf_hi(e2);
                     w[k][i] = e2;
@@ -289,6 +315,7 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
         const float sum = rb(acc);
+        const float rsum = __frcp_rn(sum);
         uint4* orow = reinterpret_cast<uint4*>(out + row * cols);
 #pragma unroll
         for (int k = 0; k < kSmMaxVec; ++k) {
@@ -296,7 +323,12 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
             if (c < nchunk) {
                 uint32_t o[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[i] = rb2(__fdiv_rn(bf_lo(w[k][i]), sum), __fdiv_rn(bf_hi(w[k][i]), sum));
+                for (int i = 0; i < 4; ++i) {
+                    const float e0 = bf_lo(w[k][i]), e1 = bf_hi(w[k][i]);
+                    const float q0 = fabsf(e0) < 1e-30f ? __fdiv_rn(e0, sum) : e0 * rsum;
+                    const float q1 = fabsf(e1) < 1e-30f ? __fdiv_rn(e1, sum) : e1 * rsum;
+                    o[i] = rb2(q0, q1);
+                }
                 orow[c] = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
@@ -357,10 +389,23 @@ extern "C" int mxq_softmax_bf16(const void* x, void* out, int64_t rows, int64_t 
     if (!x || !out) return MXQ_ERR_BAD_ARG;
     if (cols % 8 != 0 || cols > kSmMaxVec * 256) return MXQ_ERR_UNSUPPORTED;
     if (!aligned16(x) || !aligned16(out)) return MXQ_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint16_t* xs = (const uint16_t*)x;
+    uint16_t* os = (uint16_t*)out;
+    if (!use_exp2 && rows * cols >= ((int64_t)1 << 22)) {
+        // large inputs: exp from the table, persistent CTAs
+        const uint16_t* table = bf16_table<1>();
+        auto kern = softmax_bf16_kernel<false, true>;
+        if (table && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTabBytes) == cudaSuccess) {
+            const int64_t ctas = (rows + kTabThreads / 32 - 1) / (kTabThreads / 32);
+            kern<<<(unsigned)std::min<int64_t>(ctas, sm_count()), kTabThreads, kTabBytes, st>>>(xs, os, table, rows, (int)cols);
+            return check_launch();
+        }
+        cudaGetLastError();
+    }
     const int64_t ctas = (rows + kSmThreads / 32 - 1) / (kSmThreads / 32);
     const unsigned grid = (unsigned)std::min<int64_t>(ctas, (int64_t)sm_count() * 8);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (use_exp2) softmax_bf16_kernel<true><<<grid, kSmThreads, 0, st>>>((const uint16_t*)x, (uint16_t*)out, rows, (int)cols);
-    else softmax_bf16_kernel<false><<<grid, kSmThreads, 0, st>>>((const uint16_t*)x, (uint16_t*)out, rows, (int)cols);
+    if (use_exp2) softmax_bf16_kernel<true, false><<<grid, kSmThreads, 0, st>>>(xs, os, nullptr, rows, (int)cols);
+    else softmax_bf16_kernel<false, false><<<grid, kSmThreads, 0, st>>>(xs, os, nullptr, rows, (int)cols);
     return check_launch();
 }

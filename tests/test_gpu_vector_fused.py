@@ -129,6 +129,33 @@ def test_softmax(monkeypatch, shape, exp2):
     assert bool(((got - want).abs() <= 2 * ulp).all())
 
 
+def test_softmax_large_input_uses_the_table_and_matches(monkeypatch):
+    """>= 4 Mi elements: exp from the table and e * (1/s) instead of e / s; same rows as the composed chain."""
+    torch.manual_seed(21)
+    x = (torch.randn(4096, 1024, device="cuda") * 4).to(torch.bfloat16)
+    x[5, :100] = -120.0                                   # exp underflows into the subnormals and to zero
+    x[6, 0] = 80.0
+    got = mx.softmax(x, dim=-1, mx_specs=SP).float()
+    want = composed(monkeypatch, lambda: mx.softmax(x, dim=-1, mx_specs=SP)).float()
+    row_equal = (got == want).all(dim=1)
+    assert float(row_equal.float().mean()) >= 0.95, float(row_equal.float().mean())
+    ulp = want.abs().clamp_min(1e-38) * 2.0 ** -7
+    assert bool(((got - want).abs() <= 2 * ulp + 1e-38).all())
+
+
+def test_reciprocal_multiply_rounds_like_division_for_bf16_operands():
+    """The identity the softmax kernel relies on: for bfloat16 e in (0, 1] and s in [1, 2048],
+    bf16(e * fl(1/s)) == bf16(e / s) whenever the quotient is a normal bfloat16 number."""
+    e = all_bf16_patterns()
+    e = e[(e > 0) & (e <= 1) & (e.float() >= 1e-30)].float()
+    s = all_bf16_patterns()
+    s = s[(s >= 1) & (s <= 2048)].float()
+    for chunk in s.split(64):
+        q_div = (e[:, None] / chunk[None, :]).to(torch.bfloat16)
+        q_mul = (e[:, None] * (1.0 / chunk)[None, :]).to(torch.bfloat16)
+        assert torch.equal(q_div, q_mul)
+
+
 def test_softmax_nan_row_and_wide_rows_fall_back(monkeypatch):
     x = torch.randn(4, 64, device="cuda").to(torch.bfloat16)
     x[1, 5] = float("nan")
