@@ -166,6 +166,11 @@ int mxq_reduce_max_inner(const void* in, void* out, int64_t rows, int64_t inner,
  *   calls, whose summation order is unspecified).  bias, x_norm [rows, hidden]
  *   and rms_inv [rows] may be NULL.  hidden % 8 == 0 needs 16-byte aligned
  *   pointers; other widths take an element-wise path.
+ * Large inputs (>= 4 Mi elements) of mxq_silu_bf16 and mxq_softmax_bf16, and every call of
+ * mxq_swiglu_quantize_mx, read the sigmoid chain / exp from a table over all 65536 bfloat16 bit
+ * patterns that the first such call on a device builds by running the chain itself (one cudaMalloc of
+ * 128 KB, one kernel on the default stream, one synchronize; kept until exit).  Make that first
+ * call outside stream capture.
  * mxq_softmax_bf16: SoftmaxFunction.forward over the last dimension (mx/softmax.py:18-41)
  *   m = max(x); d = x - m; e = exp(d) (exp2(d) if use_exp2); s = sum(e); out = e / s;
  *   the row sum is accumulated in fp32 and rounded once.  cols % 8 == 0, cols <= 2048
