@@ -1,8 +1,8 @@
 """Regenerates the fixtures in this folder from the reference implementation.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of microsoft/microxcaling is available (--ref gives its path):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <checkout>]
 
 It writes three files beside itself:
 
