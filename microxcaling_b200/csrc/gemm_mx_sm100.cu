@@ -79,6 +79,7 @@ struct GemmArgs {
     int epi_kind;               // 0/1/2: bf16 out, bfloat16 rounding nearest/floor/even, no bias; 3: generic
     int bf16_exact;             // rounded values are bf16 values: pack upper halves
     int c_tma;                  // output written by TMA stores (row pitch multiple of 16 bytes)
+    int group_m;                // tile-rows per raster group
     int64_t rows_per_dest;      // > 0: output rows [d * rows_per_dest, (d+1) * rows_per_dest) go to destination d
 };
 
@@ -113,11 +114,11 @@ __device__ __forceinline__ void tile_coords(int64_t t, const GemmArgs& g, int64_
                                             int64_t& bi, int64_t& mt, int64_t& nt) {
     bi = t / tiles_per_batch;
     const int64_t r = t % tiles_per_batch;
-    const int64_t per_group = (int64_t)kGroupM * g.n_tiles;
+    const int64_t per_group = (int64_t)g.group_m * g.n_tiles;
     const int64_t grp = r / per_group;
     const int64_t i = r % per_group;
-    const int64_t rows = min((int64_t)kGroupM, g.m_tiles - grp * kGroupM);
-    mt = grp * kGroupM + i % rows;
+    const int64_t rows = min((int64_t)g.group_m, g.m_tiles - grp * g.group_m);
+    mt = grp * g.group_m + i % rows;
     nt = i / rows;
 }
 
@@ -715,6 +716,8 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     g.status = status_word;
     if (!g.status) return MXQ_ERR_CUDA;
     g.M = M; g.N = N; g.K = K; g.batch = batch;
+    static const int group_env = [] { const char* e = getenv("MXQ_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
+    g.group_m = group_env > 0 ? group_env : kGroupM;
     g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = (K + kBK - 1) / kBK;
     g.sfa_rows128 = (M + 127) / 128; g.sfb_rows128 = (N + 127) / 128;
     g.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, kBM, bn);
