@@ -622,9 +622,16 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             const int rows = (int)min((int64_t)a.block, a.axis_len - row0);
             const int64_t base = (p * a.axis_len + row0) * a.post + col;       // element index
             uint2 raw[kMaxRows];
+            const bool full = rows == kMaxRows;                                // a ragged last block goes the slow way
+            if (full) {
 #pragma unroll
-            for (int r = 0; r < kMaxRows; ++r)
-                raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
+                for (int r = 0; r < kMaxRows; ++r)
+                    raw[r] = __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post));
+            } else {
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r)
+                    raw[r] = r < rows ? __ldg(reinterpret_cast<const uint2*>(in + base + (int64_t)r * a.post)) : make_uint2(0, 0);
+            }
             uint32_t m0 = 0, m1 = 0;
 #pragma unroll
             for (int r = 0; r < kMaxRows; ++r) {
@@ -635,7 +642,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             FastBlock fb[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) fb[i] = fast_block(eraw[i], a);
-            const bool all_ok = fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
+            const bool all_ok = full && fb[0].ok && fb[1].ok && fb[2].ok && fb[3].ok;
             if (CK != CK_NONE) {
                 uint32_t E[4] = {fb[0].E, fb[1].E, fb[2].E, fb[3].E};
                 if (!all_ok) {
@@ -678,12 +685,12 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
                         float q[4];
                         const uint32_t o0 = quant_pair_bf16<MODE, false>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
                         const uint32_t o1 = quant_pair_bf16<MODE, false>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);
-                        if (WANT_DQ && r < rows)
+                        if (WANT_DQ)
                             *reinterpret_cast<uint2*>(out + base + (int64_t)r * a.post) = make_uint2(o0, o1);
                         if (CK != CK_NONE) {
                             c4[rr] = code_quad<CK>(fminf(q[0], fb[0].maxn) * inv[0], fminf(q[1], fb[1].maxn) * inv[1],
                                                    fminf(q[2], fb[2].maxn) * inv[2], fminf(q[3], fb[3].maxn) * inv[3], raw[r].x, raw[r].y);
-                            if (!TRANSPOSED && r < rows)
+                            if (!TRANSPOSED)
                                 *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c4[rr];
                         }
                     }
@@ -872,7 +879,7 @@ int dispatch_dt(const MxArgs& a, cudaStream_t st) {
         }
     }
     if (fast_math && a.post > 1 && a.block <= kMaxRows && a.post % N8 == 0 && ptrs8) {
-        if (DT == DT_BF16 && P <= 8 && (!a.codes || (a.fmt.ebits != 0 && (!a.transposed || (aligned16(a.codes) && a.block == kMaxRows)) && (!a.sf_gemm || !a.scales || (reinterpret_cast<uintptr_t>(a.scales) & 3u) == 0)))) {
+        if (DT == DT_BF16 && P <= 8 && a.block == kMaxRows && (!a.codes || (a.fmt.ebits != 0 && (!a.transposed || aligned16(a.codes)) && (!a.sf_gemm || !a.scales || (reinterpret_cast<uintptr_t>(a.scales) & 3u) == 0)))) {
             switch (a.mode) {
                 case RN_AWAY: return launch_strided_bf16<RN_AWAY>(a, st);
                 case RZ:      return launch_strided_bf16<RZ>(a, st);
