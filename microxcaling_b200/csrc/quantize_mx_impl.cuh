@@ -477,10 +477,10 @@ constexpr int kLastBfUnroll = 4;
 // then persistent, 1024 threads per SM, one table load per CTA.
 constexpr int kSwigluThreads = 1024;
 
-template <int MODE, bool WANT_DQ, int CK, int PRO>
-__device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_t nvec, const int lanes_per_block,
-                                                   const int row_local, const int64_t tile_base,
-                                                   const uint16_t* sig_tab) {
+template <int MODE, bool WANT_DQ, int CK, int PRO, bool FULL>
+__device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const int64_t nvec, const int lanes_per_block,
+                                                        const int row_local, const int64_t tile_base,
+                                                        const uint16_t* sig_tab) {
     const int lane_shift = 31 - __clz(lanes_per_block);
     const int64_t base = tile_base + (threadIdx.x >> 5) * (32 * kLastBfUnroll) + (threadIdx.x & 31);
     uint4 raw[kLastBfUnroll];
@@ -488,7 +488,7 @@ __device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_
 #pragma unroll
     for (int u = 0; u < kLastBfUnroll; ++u) {
         const int64_t v = base + u * 32;
-        live[u] = v < nvec;
+        live[u] = FULL || v < nvec;
         raw[u] = live[u] ? __ldg(reinterpret_cast<const uint4*>(a.in) + v) : make_uint4(0, 0, 0, 0);
     }
     if (PRO == 1) {
@@ -560,6 +560,17 @@ __device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_
             reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(c[0], c[1]);
         }
     }
+}
+
+// FULL tiles (every vector inside the tensor) run without bounds predicates.
+template <int MODE, bool WANT_DQ, int CK, int PRO>
+__device__ __forceinline__ void lastaxis_bf16_tile(const MxArgs& a, const int64_t nvec, const int lanes_per_block,
+                                                   const int row_local, const int64_t tile_base,
+                                                   const uint16_t* sig_tab) {
+    if (tile_base + (int64_t)blockDim.x * kLastBfUnroll <= nvec)
+        lastaxis_bf16_tile_impl<MODE, WANT_DQ, CK, PRO, true>(a, nvec, lanes_per_block, row_local, tile_base, sig_tab);
+    else
+        lastaxis_bf16_tile_impl<MODE, WANT_DQ, CK, PRO, false>(a, nvec, lanes_per_block, row_local, tile_base, sig_tab);
 }
 
 template <int MODE, bool WANT_DQ, int CK, int PRO = 0>
