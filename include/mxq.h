@@ -140,6 +140,23 @@ int mxq_quantize_elemwise_host(const void* h_in, void* h_out, int in_dtype, int 
 int64_t mxq_host_workspace_bytes(void);
 
 /*
+ * The two quantizers on the HOST cores, for tensors in ordinary host memory
+ * (no GPU is touched).  Replace quantize_mx_func_cpp (mx/cpp/funcs.cpp:23-98,
+ * loop mx/cpp/funcs.h:61-100) and quantize_elemwise_func_cpp
+ * (mx/cpp/funcs.cpp:117-149), which the reference calls for CPU tensors when
+ * custom_cuda is set (mx/mx_ops.py:259-263, mx/elemwise_ops.py:122-124).
+ * Arguments as in mxq_quantize_mx / mxq_quantize_elemwise without the packed
+ * outputs; all pointers are host pointers; results equal the GPU kernels'.
+ * nthreads: OpenMP threads to use, 0 = all (the reference's loop is single-threaded).
+ */
+int mxq_cpu_quantize_mx(const void* in, void* out, int dtype, int64_t pre, int64_t axis_len, int64_t post,
+                        int block, int scale_bits, int elem_ebits, int elem_mbits, float elem_max_norm,
+                        int flush_fp32_subnorms, int rmode, const void* noise, int nthreads);
+int mxq_cpu_quantize_elemwise(const void* in, void* out, int in_dtype, int out_dtype, int64_t n, int bits,
+                              int exp_bits, float max_norm, int rmode, int saturate_normals, int allow_denorm,
+                              const void* noise, int nthreads);
+
+/*
  * Sum / max over the innermost dimension of an fp32 [rows, inner] matrix into
  * out[rows].  Replace reduce_sum_inner_dim / reduce_max_inner_dim
  * (mx/cpp/funcs.cpp:219-231, mx/cpp/reduce.cu:15-89).  Any inner >= 1 is

@@ -61,6 +61,8 @@ def lib():
                                           i32, i32, i32, vp]
         L.mxq_sum_slabs_f32.argtypes = [vp, i32, i64, vp, vp]
         L.mxq_rmsnorm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
+        L.mxq_cpu_quantize_mx.argtypes = [vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32, i32, i32, vp, i32]
+        L.mxq_cpu_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, i32]
         _lib = L
     return _lib
 
@@ -240,6 +242,55 @@ def quantize_elemwise_host(A, bits, exp_bits, max_norm, rmode=0, saturate_normal
                                                    int(bool(allow_denorm)), _ptr(ws), ws.numel(),
                                                    ctypes.c_void_p(st.cuda_stream)))
             st.synchronize()
+    return out
+
+
+def _require_cpu(t, name="tensor"):
+    if t.is_cuda or t.layout != torch.strided:
+        raise MxqError("%s must be a dense CPU tensor" % name)
+    if t.dtype not in _DT:
+        raise MxqError("Tensor dtype not supported: %s" % t.dtype)
+
+
+def cpu_quantize_mx(A, scale_bits, ebits, mbits, max_norm, block, axis, flush=False, rmode=0, noise=None,
+                    nthreads=0):
+    """MX-quantize a CPU tensor on the host cores (mxq_cpu_quantize_mx); same results as the GPU kernels."""
+    _require_cpu(A, "A")
+    A = A.contiguous()
+    out = torch.empty_like(A)
+    if A.numel() == 0:
+        return out
+    axis = axis % A.dim()
+    pre, n, post = _split(list(A.shape), axis)
+    if noise is not None:
+        noise = noise.to(torch.float32).contiguous()
+        assert noise.shape == A.shape and not noise.is_cuda
+    check(lib().mxq_cpu_quantize_mx(ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(out.data_ptr()), _DT[A.dtype],
+                                    pre, n, post, int(block) if block and block > 0 else n, int(scale_bits),
+                                    int(ebits), int(mbits), float(max_norm), int(bool(flush)), int(rmode),
+                                    ctypes.c_void_p(noise.data_ptr()) if noise is not None else None, int(nthreads)))
+    return out
+
+
+def cpu_quantize_elemwise(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=False, allow_denorm=True,
+                          noise=None, out_dtype=None, nthreads=0):
+    """Elementwise rounding of a CPU tensor on the host cores (mxq_cpu_quantize_elemwise)."""
+    _require_cpu(A, "A")
+    if bits > 24:
+        raise MxqError("quantize_elemwise with bits > 24 leads to negative shifts")
+    A = A.contiguous()
+    out = torch.empty_like(A) if out_dtype in (None, A.dtype) else torch.empty(A.shape, dtype=out_dtype)
+    if A.numel() == 0:
+        return out
+    if noise is not None:
+        noise = noise.to(torch.float32).contiguous()
+        assert noise.shape == A.shape and not noise.is_cuda
+    check(lib().mxq_cpu_quantize_elemwise(ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                          _DT[A.dtype], _DT[out.dtype], A.numel(), int(bits), int(exp_bits),
+                                          float(max_norm), int(rmode), int(bool(saturate_normals)),
+                                          int(bool(allow_denorm)),
+                                          ctypes.c_void_p(noise.data_ptr()) if noise is not None else None,
+                                          int(nthreads)))
     return out
 
 
@@ -453,10 +504,20 @@ class _Funcs:
         return quantize_elemwise(A, bits, exp_bits, max_norm, int(rmode), saturate_normals, allow_denorm)
 
     @staticmethod
-    def quantize_mx_func_cpp(*args, **kwargs):
-        raise MxqError("this back-end has no host (C++) quantizer: move the tensor to a CUDA device")
+    def quantize_mx_func_cpp(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm, max_values, axis,
+                             flush_fp32_subnorms=False, rmode=0):
+        # the whole `axis` is one block (the caller reshaped to blocks); its maximum is recomputed
+        if not 1 <= A.dim() <= 5:
+            raise MxqError("quantize_mx_func_cpp needs a tensor of 1 to 5 dimensions")
+        if axis >= A.dim():
+            raise MxqError("quantize_mx_func_cpp axis exceeds input dimensions")
+        return cpu_quantize_mx(A, scale_bits, elem_ebits, elem_mbits, elem_max_norm, 0, axis, flush_fp32_subnorms,
+                               int(rmode))
 
-    quantize_elemwise_func_cpp = quantize_mx_func_cpp
+    @staticmethod
+    def quantize_elemwise_func_cpp(A, bits, exp_bits, max_norm, rmode=0, saturate_normals=False,
+                                   allow_denorm=True):
+        return cpu_quantize_elemwise(A, bits, exp_bits, max_norm, int(rmode), saturate_normals, allow_denorm)
 
     @staticmethod
     def reduce_sum_inner_dim(A):

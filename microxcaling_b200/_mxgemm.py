@@ -9,13 +9,13 @@ length not a multiple of 32) follows the reference's construction: fake-quantize
 both operands, multiply with torch, round the result
 (mx/linear.py:62-96, mx/matmul.py:68-96, mx/bmm.py:40-62).
 """
-import weakref
-
 import torch
 
 from .elemwise_ops import quantize_elemwise_op
 from .formats import ElemFormat, _get_format_params
+from .matmul_precision import set_matmul_precision
 from .mx_ops import quantize_mx_op
+from .packed import PackedMX
 
 _MODE = {"nearest": 0, "floor": 1, "even": 2}
 _torch_matmul = torch.matmul
@@ -44,57 +44,20 @@ def _fast_ok(in1, in2, f1, f2, specs, K, r1, r2, out_round):
 
 
 def _pack(x, fmt, specs, rnd, contraction_last):
-    """x [..., R, K] (contraction_last) or [..., K, R] -> codes [batch, R, K], scales, container id."""
-    from . import _backend as be
-    ebits, mbits, _, max_norm, _ = _get_format_params(fmt)
-    scale_bits = specs["scale_bits"] or 8
-    x = x.contiguous()
-    if contraction_last:
-        R, K = x.shape[-2], x.shape[-1]
-        x2 = x.reshape(-1, K)
-        _, codes, scales = be.quantize_mx(x2, scale_bits, ebits, mbits, max_norm, 32, 1,
-                                          specs["mx_flush_fp32_subnorms"], _MODE[rnd], want_dq=False,
-                                          want_codes=True, gemm_layout=True, rows_per_batch=R)
-    else:
-        K, R = x.shape[-2], x.shape[-1]
-        x3 = x.reshape(-1, K, R)
-        _, codes, scales = be.quantize_mx(x3, scale_bits, ebits, mbits, max_norm, 32, 1,
-                                          specs["mx_flush_fp32_subnorms"], _MODE[rnd], want_dq=False,
-                                          want_codes=True, transposed=True, gemm_layout=True)
-    return codes, scales, (1 if ebits == 5 else 0)
-
-
-# Packed right operands of inference calls, per source tensor: the reference re-quantizes a layer's
-# weight on every forward (mx/linear.py:40-47,83); when nothing needs a gradient and the tensor is unchanged since
-# the last call (same storage, same version counter, same format and rounding) the packed operand
-# is reused instead.  One entry per source tensor, dropped with it.
-_PACK_CACHE = {}          # id(source tensor) -> (weak reference, key, packed operand)
-
-
-def _pack_cached(src, x, fmt, specs, rnd, contraction_last):
-    """_pack(x, ...) where x derives from the long-lived tensor `src` (a layer weight)."""
-    if src is None or not x.is_cuda:
-        return _pack(x, fmt, specs, rnd, contraction_last)
-    key = (src.data_ptr(), src._version, x.dtype, tuple(x.shape), str(fmt), rnd, contraction_last, specs["scale_bits"],
-           specs["mx_flush_fp32_subnorms"], specs["bfloat"], specs["fp"], specs["round_weight"])
-    sid = id(src)
-    hit = _PACK_CACHE.get(sid)
-    if hit is not None and hit[0]() is src and hit[1] == key:
-        return hit[2]
-    packed = _pack(x, fmt, specs, rnd, contraction_last)
-    _PACK_CACHE[sid] = (weakref.ref(src, lambda _r, sid=sid: _PACK_CACHE.pop(sid, None)), key, packed)
-    return packed
+    """x [..., R, K] (contraction_last) or [..., K, R] -> PackedMX with batch = the leading dimensions."""
+    return PackedMX.quantize(x, fmt, specs, round=rnd, contraction_last=contraction_last)
 
 
 def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, trans1=False, trans2=False,
-            in2_source=None):
+            in1_packed=None, in2_packed=None):
     """op1(in1) @ op2(in2), op(x) = x^T of the last two dims when trans is set.
 
     in1: [..., M, K] (or [..., K, M] with trans1); in2: [..., K, N] (or [..., N, K] with trans2),
     in2 may have fewer leading dims than in1 (a shared 2-D matrix).  `bias` is an
-    already-quantized vector added after the first output rounding.  `in2_source`: the
-    long-lived tensor in2 was derived from (a layer's weight); callers pass it only for
-    inference calls, which may then reuse its packed form."""
+    already-quantized vector added after the first output rounding.  `in1_packed` /
+    `in2_packed`: a PackedMX holding the operand already quantized with (fmt, round) along the
+    contraction axis (a frozen layer weight, or probabilities packed by the fused softmax);
+    the tensor argument then only supplies shape, dtype and device."""
     fmt1, fmt2 = _fmt(fmt1), _fmt(fmt2)
     M, K = (in1.shape[-1], in1.shape[-2]) if trans1 else (in1.shape[-2], in1.shape[-1])
     N, K2 = (in2.shape[-2], in2.shape[-1]) if trans2 else (in2.shape[-1], in2.shape[-2])
@@ -108,23 +71,27 @@ def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, t
         fast = False
     if fast:
         from . import _backend as be
-        a_codes, a_scales, ka = _pack(in1, fmt1, specs, round1, not trans1)
-        b_codes, b_scales, kb = _pack_cached(in2_source, in2, fmt2, specs, round2, trans2)
         if shared_b:
             batch, rows = 1, in1.numel() // K       # leading dims of in1 fold into M
-            if rows != M:
-                # scales were laid out per [M]-row batch element; redo with all rows in one batch
-                a_codes, a_scales, ka = _pack(in1.reshape(-1, K), fmt1, specs, round1, True)
         else:
             batch, rows = (in1.numel() // (M * K)), M
+        a = in1_packed
+        if a is None:
+            # with a shared right operand the scales are laid out for all rows in one batch element
+            a = _pack(in1.reshape(-1, K) if shared_b else in1, fmt1, specs, round1, not trans1)
+        b = in2_packed if in2_packed is not None else _pack(in2, fmt2, specs, round2, trans2)
+        if a.batch * a.rows != batch * rows or a.K != K or b.rows != N or b.K != K or b.batch != batch:
+            raise ValueError("packed operand does not match the product's shape")
         bits = specs["bfloat"] if specs["bfloat"] >= 10 else 0
-        out = be.gemm_mx(a_codes, a_scales, b_codes, b_scales, batch, rows, N, K, ka, kb,
+        out = be.gemm_mx(a.codes, a.scales, b.codes, b.scales, batch, rows, N, K, a.container, b.container,
                          out_dtype=in1.dtype if in1.dtype != torch.float16 else torch.float32,
                          bfloat_bits=bits, round_mode=_MODE[out_round],
                          bias=None if bias is None else bias.reshape(-1))
         if in1.dtype == torch.float16:
             out = out.to(torch.float16)
         return out.reshape(*lead1, M, N)
+    if in1_packed is not None or in2_packed is not None:
+        raise ValueError("a packed operand needs the tensor-core path (CUDA tensors, FP formats, block size 32)")
 
     # reference construction
     q1 = quantize_mx_op(in1, specs, elem_format=fmt1, axes=[-2 if trans1 else -1], round=round1)
@@ -133,7 +100,8 @@ def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, t
         q2 = q2.to(q1.dtype)
     a = q1.transpose(-1, -2) if trans1 else q1
     b = q2.transpose(-1, -2) if trans2 else q2
-    out = _torch_matmul(a, b)
+    with set_matmul_precision(a, b, fmt1, fmt2):
+        out = _torch_matmul(a, b)
     out = quantize_elemwise_op(out, mx_specs=specs, round=out_round)
     if bias is not None:
         out = quantize_elemwise_op(out + bias, mx_specs=specs, round=out_round)

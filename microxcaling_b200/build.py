@@ -18,7 +18,7 @@ OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libmxq.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--threads", "2"]
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-fopenmp", "--threads", "2"]
 
 
 def _newest_header():
@@ -52,7 +52,7 @@ def build(force=False, verbose=False):
                 if verbose:
                     sys.stderr.write(log)
     if todo or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcuda"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcuda", "-lgomp"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stderr)

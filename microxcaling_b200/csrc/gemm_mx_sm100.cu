@@ -26,20 +26,22 @@
 #include <cuda.h>
 #include <algorithm>
 #include <cstring>
-#include <cstdlib>
+#include <mutex>
 #include "mxq_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 
 namespace mxq {
 
-#ifdef MXQ_GEMM_TRACE
-#define TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 1000) { long long c_ = clock64(); reinterpret_cast<long long*>(g.status + 16)[slot] = c_; } } while (0)
-#else
-#define TRACE(slot) do {} while (0)
+// Operand stages of the CTA-pair kernel (5 leaves room for 128-byte-wide output boxes).
+#ifndef MXQ_PAIR_STAGES
+#define MXQ_PAIR_STAGES 5
+#endif
+#ifndef MXQ_PAIR_BOX
+#define MXQ_PAIR_BOX 128
 #endif
 
-constexpr int kBM = 128;          // tile rows (MMA M)
+constexpr int kBM = 128;          // tile rows (MMA M per CTA)
 constexpr int kBK = 128;          // K bytes per stage = four MMA K steps
 constexpr int kEpiWarps = 8;       // two per tensor-memory lane quarter
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
@@ -60,9 +62,6 @@ __device__ __forceinline__ uint32_t round_out_bits(uint32_t u, const OutRound& k
     r = mag >= kInf ? mag : r;                    // Inf / NaN pass through
     return r | (u & 0x80000000u);
 }
-__device__ __forceinline__ float round_out_f(float v, const OutRound& k) {
-    return __uint_as_float(round_out_bits(__float_as_uint(v), k));
-}
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -77,7 +76,6 @@ struct GemmArgs {
     int out_dtype;              // DT_F32 or DT_BF16
     OutRound rnd;               // bfloat rounding of the result
     int epi_kind;               // 0/1/2: bf16 out, bfloat16 rounding nearest/floor/even, no bias; 3: generic
-    int bf16_exact;             // rounded values are bf16 values: pack upper halves
     int c_tma;                  // output written by TMA stores (row pitch multiple of 16 bytes)
     int group_m;                // tile-rows per raster group
     int64_t rows_per_dest;      // > 0: output rows [d * rows_per_dest, (d+1) * rows_per_dest) go to destination d
@@ -93,15 +91,19 @@ struct OutMaps {
     CUtensorMap m[kMaxDests];
 };
 
-template <int BN, int STAGES>
+// Shared memory of the single-CTA kernel.  The epilogue staging ring holds, per
+// epilogue warp, NBUF boxes of 32 rows x BOX bytes (BOX = 64 or 128, swizzled
+// like the output tensor map).
+template <int BN, int STAGES, int BOX, int NBUF>
 struct GemmSmem {
     static constexpr int kA = kBM * kBK;
     static constexpr int kB = BN * kBK;
     static constexpr int kSFA = kSfChunk;
     static constexpr int kSFB = (BN / 128) * kSfChunk;
     static constexpr int kStage = kA + kB + kSFA + kSFB;
-    static constexpr int kStgOff = STAGES * kStage;        // per epilogue warp: [32 rows x 64 bytes]
-    static constexpr int kBarOff = kStgOff + kEpiWarps * 2048;
+    static constexpr int kStgOff = (STAGES * kStage + 1023) / 1024 * 1024;
+    static constexpr int kStgWarp = 32 * BOX * NBUF;
+    static constexpr int kBarOff = kStgOff + kEpiWarps * kStgWarp;
     static constexpr int kTotal = kBarOff + 256 + 1024;   // barriers + alignment slack
 };
 
@@ -122,92 +124,123 @@ __device__ __forceinline__ void tile_coords(int64_t t, const GemmArgs& g, int64_
     nt = i / rows;
 }
 
-// Rounds one epilogue warp's share of an accumulator tile (kCols = BN / 2 columns of 32 rows,
-// already in registers) and stores it: 64-byte chunks through a swizzled staging tile and TMA
-// stores (which clip ragged edges), or plain stores when the row pitch is not a multiple of 16 bytes.
-template <int BN>
-__device__ __forceinline__ void round_and_store(const uint32_t* v, const int half, const int lane, const uint32_t stg,
-                                                const GemmArgs& g, const CUtensorMap* tmap_c, const int64_t row0,
-                                                const int64_t row0_dest, const int64_t nt, const int64_t bi) {
-    constexpr int kCols = BN / 2;
-    const bool f32_out = g.out_dtype == DT_F32;
+// Rounds one chunk of accumulator columns of a row (v) to the BOX / 4 output words (w) of that row:
+// BOX / 4 fp32 columns, or BOX / 2 columns packed two bfloat16 to a word.
+template <int BOX, bool F32>
+__device__ __forceinline__ void round_chunk(const uint32_t* v, uint32_t* w, const GemmArgs& g, const int64_t col0) {
+    constexpr int W = BOX / 4;
     const float* bp = reinterpret_cast<const float*>(g.bias);
+    if (F32) {
 #pragma unroll
-    for (int cc = 0; cc < kCols; cc += 32) {
-        // 32 accumulator columns: one 64-byte chunk of bf16 or two of fp32
+        for (int i = 0; i < W; ++i) {
+            uint32_t b = round_out_bits(v[i], g.rnd);
+            if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
+            w[i] = b;
+        }
+    } else if (g.epi_kind == 0) {              // half away: add half an ulp of bf16, keep the upper halves
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-            if (!f32_out && sub == 1) break;
-            const int c0 = half * kCols + cc + sub * 16;
-            const int64_t col0 = nt * BN + c0;
-            if (col0 >= g.N) break;
-            uint32_t w[16];
-            if (f32_out) {
+        for (int i = 0; i < W; ++i) w[i] = __byte_perm(v[2 * i] + 0x8000u, v[2 * i + 1] + 0x8000u, 0x7632);
+    } else if (g.epi_kind == 1) {              // toward zero
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    uint32_t b = round_out_bits(v[cc + sub * 16 + i], g.rnd);
-                    if (bp) b = round_out_bits(__float_as_uint(__uint_as_float(b) + __ldg(bp + min(col0 + i, g.N - 1))), g.rnd);
-                    w[i] = b;
-                }
-            } else if (g.epi_kind == 0) {              // half away: add half an ulp of bf16, keep the upper halves
+        for (int i = 0; i < W; ++i) w[i] = __byte_perm(v[2 * i], v[2 * i + 1], 0x7632);
+    } else if (g.epi_kind == 2) {              // half even: the hardware conversion
 #pragma unroll
-                for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i] + 0x8000u, v[cc + 2 * i + 1] + 0x8000u, 0x7632);
-            } else if (g.epi_kind == 1) {              // toward zero
+        for (int i = 0; i < W; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) w[i] = __byte_perm(v[cc + 2 * i], v[cc + 2 * i + 1], 0x7632);
-            } else if (g.epi_kind == 2) {              // half even: the hardware conversion
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[cc + 2 * i]), __uint_as_float(v[cc + 2 * i + 1]));
-                    w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    uint32_t b0 = round_out_bits(v[cc + 2 * i], g.rnd);
-                    uint32_t b1 = round_out_bits(v[cc + 2 * i + 1], g.rnd);
-                    if (bp) {
-                        b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
-                        b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
-                    }
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b0), __uint_as_float(b1));
-                    w[i] = *reinterpret_cast<const uint32_t*>(&h);
-                }
+        for (int i = 0; i < W; ++i) {
+            uint32_t b0 = round_out_bits(v[2 * i], g.rnd);
+            uint32_t b1 = round_out_bits(v[2 * i + 1], g.rnd);
+            if (bp) {
+                b0 = round_out_bits(__float_as_uint(__uint_as_float(b0) + __ldg(bp + min(col0 + 2 * i, g.N - 1))), g.rnd);
+                b1 = round_out_bits(__float_as_uint(__uint_as_float(b1) + __ldg(bp + min(col0 + 2 * i + 1, g.N - 1))), g.rnd);
             }
-            if (g.c_tma) {
-                if (lane == 0) ptx::bulk_wait_read0();            // staging tile free again
-                __syncwarp();
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(b0), __uint_as_float(b1));
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    }
+}
+
+// One epilogue warp's share of an accumulator tile: kCols columns of its 32 tensor-memory lanes,
+// starting at tensor-memory address `taddr` = column `first_col` of the tile.  The columns are
+// drained in chunks of one output box (32 rows x BOX bytes): tcgen05.ld -> rounding -> swizzled
+// staging buffer -> TMA store (which clips ragged M / N edges), or plain stores when the row
+// pitch is not a multiple of 16 bytes.  The staging buffers of a warp form a ring of NBUF boxes
+// (`ring` counts boxes across tiles); a box is rewritten once the bulk store issued NBUF boxes
+// earlier has read it.  `after_first` runs when the first 32 columns have left tensor memory.
+template <int kCols, int BOX, int NBUF, bool F32, typename AfterFirst>
+__device__ __forceinline__ void drain_tile(const uint32_t taddr, const int first_col, const int lane, const uint32_t stg,
+                                           uint32_t& ring, const GemmArgs& g, const CUtensorMap* tmap_c,
+                                           const int64_t row0, const int64_t row0_dest, const int64_t tile_col0,
+                                           const int64_t bi, AfterFirst after_first) {
+    constexpr int CC = F32 ? BOX / 4 : BOX / 2;      // accumulator columns per chunk
+    constexpr int W = BOX / 4;                       // output words per row and chunk
+    static_assert(CC == 16 || CC == 32 || CC == 64, "chunk width");
+#pragma unroll 1
+    for (int c = 0; c < kCols; c += CC) {
+        uint32_t v[CC];
+        if constexpr (CC == 16) {
+            ptx::tmem_ld_32x32b_x16(taddr + c, v);
+        } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    ptx::st_shared_v4(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-                ptx::fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::tma_store_3d(tmap_c, stg, (int)col0, (int)row0_dest, (int)bi);
-                    ptx::bulk_commit();
-                }
-            } else if (row0 + lane < g.M) {
-                // row pitch not a multiple of 16 bytes: plain stores
-                const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
+            for (int j = 0; j < CC; j += 32) ptx::tmem_ld_32x32b_x32(taddr + c + j, v + j);
+        }
+        ptx::tmem_ld_wait();
+        if (c < 32 && c + CC >= 32) after_first();                // columns 0..31 have left tensor memory
+        const int64_t col0 = tile_col0 + first_col + c;
+        if (row0 >= g.M || col0 >= g.N) continue;                 // whole box outside the result (warp-uniform)
+        uint32_t w[W];
+        round_chunk<BOX, F32>(v, w, g, col0);
+        if (g.c_tma) {
+            const uint32_t buf = stg + (ring % NBUF) * (32 * BOX);
+            ++ring;
+            if (lane == 0) ptx::bulk_wait_read<NBUF - 1>();      // this box's previous store has read it
+            __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (f32_out) {
-                        if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
-                    } else {
-                        if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
-                        if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
-                    }
+            for (int q = 0; q < BOX / 16; ++q) {
+                const int sw = BOX == 128 ? (q ^ (lane & 7)) : (q ^ ((lane >> 1) & 3));
+                ptx::st_shared_v4(buf + lane * BOX + (sw << 4), w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::tma_store_3d(tmap_c, buf, (int)col0, (int)row0_dest, (int)bi);
+                ptx::bulk_commit();
+            }
+        } else if (row0 + lane < g.M) {
+            const int64_t off = (bi * g.M + row0 + lane) * g.N + col0;
+#pragma unroll
+            for (int i = 0; i < W; ++i) {
+                if (F32) {
+                    if (col0 + i < g.N) reinterpret_cast<uint32_t*>(g.c)[off + i] = w[i];
+                } else {
+                    if (col0 + 2 * i < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i] = (uint16_t)w[i];
+                    if (col0 + 2 * i + 1 < g.N) reinterpret_cast<uint16_t*>(g.c)[off + 2 * i + 1] = (uint16_t)(w[i] >> 16);
                 }
             }
         }
     }
 }
 
-template <int BN, int STAGES, int ACC_BUFS>
+// Tensor-memory columns.  Two accumulators of 256 columns fill the 512 columns completely, so the
+// scale columns of the tile being computed (4 for A, BN / 32 for B, twice that when the K blocks
+// alternate between two sets) are parked in the first 32 columns of the OTHER accumulator: the
+// previous tile's epilogue reads those columns first and hands them back (`sf_free`) long before
+// it has drained the rest, so the next tile's MMAs start almost at once.
+constexpr uint32_t kTmemCols = 512;
+// K blocks alternate between two sets of scale columns so that the copy of block j + 1's scales
+// need not wait for the MMAs of block j to have read theirs.
+constexpr uint32_t kSfSets = 2;
+constexpr uint32_t kSfSetCols = 16;
+
+template <int BN, int STAGES, int ACC_BUFS, int BOX, int NBUF>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ OutMaps tmaps_c, const GemmArgs g) {
-    using S = GemmSmem<BN, STAGES>;
+    using S = GemmSmem<BN, STAGES, BOX, NBUF>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
@@ -223,13 +256,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr uint32_t kAccCols = BN * ACC_BUFS;
-    constexpr uint32_t kTmemCols = 512;
-    // Two 256-column accumulators fill tensor memory completely.  The 12 scale columns of the tile
-    // being computed then live in the first columns of the OTHER accumulator buffer: the previous
-    // tile's epilogue hands those columns back (sf_free) as soon as it has read them, long before
-    // it has drained the rest, so the next tile's MMAs start almost at once.
-    constexpr bool kSfSwap = kAccCols + 4 + BN / 32 > kTmemCols;
+    constexpr bool kSfSwap = kAccCols + kSfSets * kSfSetCols > kTmemCols;
     static_assert(!kSfSwap || (ACC_BUFS == 2 && kAccCols == kTmemCols), "scale columns need a home");
+    static_assert(4 + BN / 32 <= kSfSetCols, "scale set width");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
@@ -279,7 +308,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         ptx::bulk_load(ptx::smem_u32(st + S::kA + S::kB + S::kSFA + j * kSfChunk),
                                        g.sfb + ((bi * g.sfb_rows128 + nt * (BN / 128) + j) * g.k_blocks + kb) * kSfChunk,
                                        kSfChunk, bar);
-                    TRACE(0 + 2 * it);
                 }
             }
             if (!ok) {
@@ -302,24 +330,24 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     !ptx::mbar_wait(ptx::smem_u32(&sf_free[buf ^ 1]), ((tile_i - 1) / ACC_BUFS) & 1, abort_flag)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
-                const uint32_t kSfaCol = kSfSwap ? (uint32_t)(buf ^ 1) * BN : kAccCols;
-                const uint32_t kSfbCol = kSfaCol + 4;
+                const uint32_t sf_home = tmem_base + (kSfSwap ? (uint32_t)(buf ^ 1) * BN : kAccCols);
                 for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!ptx::mbar_wait(ptx::smem_u32(&full[s]), ph, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after();
-                    TRACE(200 + 2 * it);
                     uint8_t* st = smem + (size_t)s * S::kStage;
                     const uint32_t a_addr = ptx::smem_u32(st);
                     const uint32_t b_addr = ptx::smem_u32(st + S::kA);
                     const uint32_t sfa_addr = ptx::smem_u32(st + S::kA + S::kB);
                     const uint32_t sfb_addr = sfa_addr + S::kSFA;
+                    const uint32_t sfa_col = sf_home + (it % kSfSets) * kSfSetCols;
+                    const uint32_t sfb_col = sfa_col + 4;
                     // scales: 32 rows x 16 bytes per chunk, 8-row groups 128 bytes apart, no swizzle
-                    ptx::tc_cp_32x128b_warpx4(tmem_base + kSfaCol, ptx::smem_desc(sfa_addr, 0, 128, 0));
+                    ptx::tc_cp_32x128b_warpx4(sfa_col, ptx::smem_desc(sfa_addr, 0, 128, 0));
 #pragma unroll
                     for (int j = 0; j < BN / 128; ++j)
-                        ptx::tc_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * j, ptx::smem_desc(sfb_addr + j * kSfChunk, 0, 128, 0));
+                        ptx::tc_cp_32x128b_warpx4(sfb_col + 4 * j, ptx::smem_desc(sfb_addr + j * kSfChunk, 0, 128, 0));
 #pragma unroll
                     for (int k = 0; k < kBK / 32; ++k) {
                         // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; a K step of
@@ -327,27 +355,23 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const uint64_t ad = ptx::smem_desc(a_addr + 32 * k, 0, 1024, 2);
                         const uint64_t bd = ptx::smem_desc(b_addr + 32 * k, 0, 1024, 2);
                         const uint32_t id = g.idesc | ((uint32_t)k << 4) | ((uint32_t)k << 29);
-                        ptx::tc_mma_mxf8f6f4(d_tmem, ad, bd, id, (tmem_base + kSfaCol) | ((uint32_t)k << 30),
-                                             (tmem_base + kSfbCol) | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                        ptx::tc_mma_mxf8f6f4(d_tmem, ad, bd, id, sfa_col | ((uint32_t)k << 30),
+                                             sfb_col | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit(ptx::smem_u32(&empty[s]));        // stage reusable once these MMAs retire
                 }
                 if (ok) ptx::tc_commit(ptx::smem_u32(&acc_full[buf]));
-                TRACE(400 + 2 * tile_i);
             }
         }
     } else {
         // ---------------- epilogue warps ----------------
-        // Warp (2 + e) drains lane quarter (warp & 3), column half (e >> 2) of the accumulator
-        // in chunks of 64 output bytes per row: tcgen05.ld -> rounding -> 64-byte-swizzled
-        // staging tile in shared memory -> TMA store (which also clips ragged M / N edges).
+        // Warp (2 + e) drains lane quarter (warp & 3), column half (e >> 2) of the accumulator.
         const int e = warp - 2;
         const int q = warp & 3;                               // the tensor-memory lane quarter this warp may read
         const int half = e >> 2;
-        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * 2048);
-        const bool f32_out = g.out_dtype == DT_F32;
-        const float* bp = reinterpret_cast<const float*>(g.bias);
-        uint32_t tile_i = 0;
+        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * S::kStgWarp);
+        constexpr int kCols = BN / 2;
+        uint32_t tile_i = 0, ring = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
             const int buf = tile_i % ACC_BUFS;
@@ -356,37 +380,26 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tile_coords(t, g, tiles_per_batch, bi, mt, nt);
             if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buf]), acc_ph, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
-            if (warp == 2 && lane == 0) TRACE(600 + 2 * tile_i);
             const int64_t row0 = mt * kBM + q * 32;
             // destination of this tile's rows (128-row tiles never straddle destinations)
             const int64_t dest = g.rows_per_dest > 0 ? row0 / g.rows_per_dest : 0;
             const int64_t row0_dest = row0 - dest * g.rows_per_dest;
-            const CUtensorMap* tmap_c = &tmaps_c.m[dest];
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN;
-            // Read this warp's whole share of the accumulator (BN/2 columns) into registers first
-            // and hand the tensor-memory buffer back to the MMA warp at once; rounding and stores
-            // then overlap the next tile's main loop even with a single accumulator buffer.
-            constexpr int kCols = BN / 2;
-            uint32_t v[kCols];
-            if (kSfSwap && half == 0) {
-                // columns 0..31 first: the next tile's scales go there
-                ptx::tmem_ld_32x32b_x32(taddr, v);
-                ptx::tmem_ld_wait();
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sf_free[buf]));
-#pragma unroll
-                for (int c = 32; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + c, v + c);
-            } else {
-#pragma unroll
-                for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
-            }
-            ptx::tmem_ld_wait();
+            const CUtensorMap* tmap_c = &tmaps_c.m[dest < kMaxDests ? dest : 0];
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + half * kCols;
+            auto after_first = [&]() {
+                if (kSfSwap && half == 0) {                   // columns 0..31 are out: the next tile's scales go there
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sf_free[buf]));
+                }
+            };
+            if (g.out_dtype == DT_F32)
+                drain_tile<kCols, BOX, NBUF, true>(taddr, half * kCols, lane, stg, ring, g, tmap_c, row0, row0_dest, nt * BN, bi, after_first);
+            else
+                drain_tile<kCols, BOX, NBUF, false>(taddr, half * kCols, lane, stg, ring, g, tmap_c, row0, row0_dest, nt * BN, bi, after_first);
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buf]));
-            if (warp == 2 && lane == 0) TRACE(800 + 2 * tile_i);
-            round_and_store<BN>(v, half, lane, stg, g, tmap_c, row0, row0_dest, nt, bi);
         }
         if (lane == 0) ptx::bulk_wait_all();
     }
@@ -407,14 +420,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // tile and the scales it needs (its rows of A, all 256 columns of B), so a K
 // block costs 33.5 KB of shared-memory fill per SM instead of 49.5 KB; the even
 // CTA issues tcgen05.cp / tcgen05.mma for both, and every CTA drains the 128
-// accumulator rows held in its own tensor memory.  Barriers: `full` lives in
-// the even CTA and counts the bytes of both CTAs' loads; `empty` and `acc_full`
-// exist in both CTAs and are signalled together by a multicast commit;
-// `acc_empty` lives in the even CTA and collects the epilogue warps of both.
+// accumulator rows held in its own tensor memory.  Two accumulators alternate
+// (the scale columns parked in the idle one, as above), so the drain of a tile
+// runs under the main loop of the next.  Barriers: `full` lives in the even
+// CTA and counts the bytes of both CTAs' loads; `empty` and `acc_full` exist in
+// both CTAs and are signalled together by a multicast commit; `acc_empty` and
+// `sf_free` live in the even CTA and collect the epilogue warps of both.
 // No load is multicast.  All waits are bounded as in the single-CTA kernel.
 // ---------------------------------------------------------------------------
 constexpr int kPairBN = 256;
-template <int STAGES>
+template <int STAGES, int BOX, int NBUF>
 struct PairSmem {
     static constexpr int kA = kBM * kBK;                   // this CTA's rows of A
     static constexpr int kB = 128 * kBK;                   // this CTA's half of the B tile
@@ -422,39 +437,41 @@ struct PairSmem {
     static constexpr int kSF = 3 * kSfChunk;               // scales: A (own rows) + B (256 columns)
     static constexpr int kStageBytes = kAB + kSF;          // bytes one CTA loads per K block
     static constexpr int kSfOff = STAGES * kAB;
-    static constexpr int kStgOff = kSfOff + STAGES * kSF;  // per epilogue warp: [32 rows x 64 bytes]
-    static constexpr int kBarOff = kStgOff + kEpiWarps * 2048;
+    static constexpr int kStgOff = (kSfOff + STAGES * kSF + 1023) / 1024 * 1024;
+    static constexpr int kStgWarp = 32 * BOX * NBUF;
+    static constexpr int kBarOff = kStgOff + kEpiWarps * kStgWarp;
     static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
-template <int STAGES>
+template <int STAGES, int BOX, int NBUF>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                     const __grid_constant__ OutMaps tmaps_c, const GemmArgs g) {
-    using S = PairSmem<STAGES>;
+    using S = PairSmem<STAGES, BOX, NBUF>;
     constexpr int BN = kPairBN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
     uint64_t* full = bars;                       // [STAGES]  used in the even CTA
     uint64_t* empty = bars + STAGES;             // [STAGES]  one per CTA
-    uint64_t* acc_full = bars + 2 * STAGES;      // one per CTA
-    uint64_t* acc_empty = acc_full + 1;          // used in the even CTA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* acc_full = bars + 2 * STAGES;      // [2]  one per CTA
+    uint64_t* acc_empty = acc_full + 2;          // [2]  used in the even CTA
+    uint64_t* sf_free = acc_empty + 2;           // [2]  used in the even CTA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_free + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();             // 0 = even CTA (issues the MMAs)
-    constexpr uint32_t kSfaCol = BN;
-    constexpr uint32_t kSfbCol = BN + 4;
-    constexpr uint32_t kTmemCols = 512;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(ptx::smem_u32(&full[s]), 1); ptx::mbar_init(ptx::smem_u32(&empty[s]), 1); }
-        ptx::mbar_init(ptx::smem_u32(acc_full), 1);
-        ptx::mbar_init(ptx::smem_u32(acc_empty), 2 * kEpiWarps);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), 2 * kEpiWarps);
+            ptx::mbar_init(ptx::smem_u32(&sf_free[b]), 2 * 4);           // the warps of both CTAs that own columns 0..31
+        }
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -494,7 +511,7 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t bar = ptx::mapa(ptx::smem_u32(&full[s]), 0);
                     const uint32_t ab = ptx::smem_u32(smem + (size_t)s * S::kAB);
                     const uint32_t sf = ptx::smem_u32(smem + S::kSfOff + (size_t)s * S::kSF);
-                    ptx::tma_load_3d_pair(ab, &tmap_a, bar, (int)(kb * kBK), (int)(mt * kBM), (int)bi);
+                                        ptx::tma_load_3d_pair(ab, &tmap_a, bar, (int)(kb * kBK), (int)(mt * kBM), (int)bi);
                     ptx::tma_load_3d_pair(ab + S::kA, &tmap_b, bar, (int)(kb * kBK), (int)(nt * BN + rank * 128), (int)bi);
                     ptx::tma_load_4d_pair(sf, &tmap_sfa, bar, 0, (int)kb, (int)mt, (int)bi);
                     ptx::tma_load_4d_pair(sf + kSfChunk, &tmap_sfb, bar, 0, (int)kb, (int)(nt * 2), (int)bi);
@@ -508,8 +525,13 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             for (int64_t t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
-                if (tile_i >= 1 && !ptx::mbar_wait(ptx::smem_u32(acc_empty), (tile_i & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint32_t buf = tile_i & 1;
+                const uint32_t acc_ph = (tile_i >> 1) & 1;
+                if (tile_i >= 2 && !ptx::mbar_wait(ptx::smem_u32(&acc_empty[buf]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                if (tile_i >= 1 && !ptx::mbar_wait(ptx::smem_u32(&sf_free[buf ^ 1]), ((tile_i - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t sf_home = tmem_base + (buf ^ 1) * BN;
                 for (int64_t kb = 0; kb < g.k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -518,20 +540,22 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t a_addr = ptx::smem_u32(smem + (size_t)s * S::kAB);
                     const uint32_t b_addr = a_addr + S::kA;
                     const uint32_t sf_addr = ptx::smem_u32(smem + S::kSfOff + (size_t)s * S::kSF);
-                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfaCol, ptx::smem_desc(sf_addr, 0, 128, 0));
-                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol, ptx::smem_desc(sf_addr + kSfChunk, 0, 128, 0));
-                    ptx::tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + 4, ptx::smem_desc(sf_addr + 2 * kSfChunk, 0, 128, 0));
+                    const uint32_t sfa_col = sf_home + (it % kSfSets) * kSfSetCols;
+                    const uint32_t sfb_col = sfa_col + 4;
+                    ptx::tc_cp_32x128b_warpx4_pair(sfa_col, ptx::smem_desc(sf_addr, 0, 128, 0));
+                    ptx::tc_cp_32x128b_warpx4_pair(sfb_col, ptx::smem_desc(sf_addr + kSfChunk, 0, 128, 0));
+                    ptx::tc_cp_32x128b_warpx4_pair(sfb_col + 4, ptx::smem_desc(sf_addr + 2 * kSfChunk, 0, 128, 0));
 #pragma unroll
                     for (int k = 0; k < kBK / 32; ++k) {
                         const uint64_t ad = ptx::smem_desc(a_addr + 32 * k, 0, 1024, 2);
                         const uint64_t bd = ptx::smem_desc(b_addr + 32 * k, 0, 1024, 2);
                         const uint32_t id = g.idesc | ((uint32_t)k << 4) | ((uint32_t)k << 29);
-                        ptx::tc_mma_mxf8f6f4_pair(tmem_base, ad, bd, id, (tmem_base + kSfaCol) | ((uint32_t)k << 30),
-                                                  (tmem_base + kSfbCol) | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                        ptx::tc_mma_mxf8f6f4_pair(d_tmem, ad, bd, id, sfa_col | ((uint32_t)k << 30),
+                                                  sfb_col | ((uint32_t)k << 30), (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit_pair(ptx::smem_u32(&empty[s]), 3);      // both CTAs may refill the stage
                 }
-                if (ok) ptx::tc_commit_pair(ptx::smem_u32(acc_full), 3);
+                if (ok) ptx::tc_commit_pair(ptx::smem_u32(&acc_full[buf]), 3);
             }
         }
     } else {
@@ -539,29 +563,35 @@ gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int e = warp - 2;
         const int q = warp & 3;
         const int half = e >> 2;
-        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * 2048);
-        const uint32_t acc_empty_even = ptx::mapa(ptx::smem_u32(acc_empty), 0);
-        uint32_t tile_i = 0;
+        const uint32_t stg = ptx::smem_u32(smem + S::kStgOff + e * S::kStgWarp);
+        constexpr int kCols = BN / 2;
+        uint32_t tile_i = 0, ring = 0;
         bool ok = true;
         for (int64_t t = pair; t < total_tiles && ok; t += n_pairs, ++tile_i) {
+            const uint32_t buf = tile_i & 1;
             int64_t bi, mt2, nt;
             tile_coords(t, g, tiles_per_batch, bi, mt2, nt);
-            if (!ptx::mbar_wait(ptx::smem_u32(acc_full), tile_i & 1, abort_flag)) { ok = false; break; }
+            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buf]), (tile_i >> 1) & 1, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
             const int64_t row0 = (2 * mt2 + rank) * kBM + q * 32;
             const int64_t dest = g.rows_per_dest > 0 ? row0 / g.rows_per_dest : 0;
             const int64_t row0_dest = row0 - dest * g.rows_per_dest;
             const CUtensorMap* tmap_c = &tmaps_c.m[dest < kMaxDests ? dest : 0];
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-            constexpr int kCols = BN / 2;
-            uint32_t v[kCols];
-#pragma unroll
-            for (int c = 0; c < kCols; c += 32) ptx::tmem_ld_32x32b_x32(taddr + half * kCols + c, v + c);
-            ptx::tmem_ld_wait();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * kCols;
+            auto after_first = [&]() {
+                if (half == 0) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&sf_free[buf]), 0));
+                }
+            };
+            if (g.out_dtype == DT_F32)
+                drain_tile<kCols, BOX, NBUF, true>(taddr, half * kCols, lane, stg, ring, g, tmap_c, row0, row0_dest, nt * BN, bi, after_first);
+            else
+                drain_tile<kCols, BOX, NBUF, false>(taddr, half * kCols, lane, stg, ring, g, tmap_c, row0, row0_dest, nt * BN, bi, after_first);
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(acc_empty_even);
-            if (row0 < g.M) round_and_store<BN>(v, half, lane, stg, g, tmap_c, row0, row0_dest, nt, bi);
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&acc_empty[buf]), 0));
         }
         if (lane == 0) ptx::bulk_wait_all();
     }
@@ -598,26 +628,31 @@ static int make_operand_map(CUtensorMap* m, const void* base, int64_t batch, int
 static int* device_status_word() {
     // one status word per device, allocated on first use and kept until exit
     static int* words[64] = {nullptr};
+    static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
     if (!words[dev]) {
-        if (cudaMalloc(&words[dev], 4096 * sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(words[dev], 0, 4096 * sizeof(int));
+        int* w = nullptr;
+        if (cudaMalloc(&w, 64) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        if (cudaMemset(w, 0, 64) != cudaSuccess) { cudaFree(w); return nullptr; }
+        words[dev] = w;
     }
     return words[dev];
 }
 
-// C [batch, M, N]: box = 64 bytes of a row x 32 rows, 64-byte swizzle
-static int make_output_map(CUtensorMap* m, void* base, int64_t batch, int64_t M, int64_t N, bool f32) {
+// C [batch, M, N]: box = box_bytes (64 or 128) of a row x 32 rows, swizzle of the same width
+static int make_output_map(CUtensorMap* m, void* base, int64_t batch, int64_t M, int64_t N, bool f32, int box_bytes) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return MXQ_ERR_CUDA;
     const cuuint64_t es = f32 ? 4 : 2;
     cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)N * es, (cuuint64_t)N * M * es};
-    cuuint32_t box[3] = {(cuuint32_t)(64 / es), 32, 1};
+    cuuint32_t box[3] = {(cuuint32_t)(box_bytes / es), 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims,
-                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
 }
@@ -636,11 +671,12 @@ static int make_sf_map(CUtensorMap* m, const void* base, int64_t batch, int64_t 
     return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_CUDA;
 }
 
-template <int STAGES>
+template <int STAGES, int BOX, int NBUF>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                             const OutMaps& tc, const GemmArgs& g, cudaStream_t st) {
-    using S = PairSmem<STAGES>;
-    auto kern = gemm_mx_pair_kernel<STAGES>;
+    using S = PairSmem<STAGES, BOX, NBUF>;
+    static_assert(S::kTotal <= 232448, "shared memory of the pair kernel");
+    auto kern = gemm_mx_pair_kernel<STAGES, BOX, NBUF>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
         return MXQ_ERR_CUDA;
     const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
@@ -659,11 +695,12 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     return check_launch();
 }
 
-template <int BN, int STAGES, int ACC_BUFS>
+template <int BN, int STAGES, int ACC_BUFS, int BOX, int NBUF>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, const GemmArgs& g,
                        cudaStream_t st) {
-    using S = GemmSmem<BN, STAGES>;
-    auto kern = gemm_mx_kernel<BN, STAGES, ACC_BUFS>;
+    using S = GemmSmem<BN, STAGES, BOX, NBUF>;
+    static_assert(S::kTotal <= 232448, "shared memory of the single-CTA kernel");
+    auto kern = gemm_mx_kernel<BN, STAGES, ACC_BUFS, BOX, NBUF>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
         return MXQ_ERR_CUDA;
     const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
@@ -716,8 +753,7 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     g.status = status_word;
     if (!g.status) return MXQ_ERR_CUDA;
     g.M = M; g.N = N; g.K = K; g.batch = batch;
-    static const int group_env = [] { const char* e = getenv("MXQ_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
-    g.group_m = group_env > 0 ? group_env : kGroupM;
+    g.group_m = kGroupM;
     g.m_tiles = (M + kBM - 1) / kBM; g.n_tiles = (N + bn - 1) / bn; g.k_blocks = (K + kBK - 1) / kBK;
     g.sfa_rows128 = (M + 127) / 128; g.sfb_rows128 = (N + 127) / 128;
     g.idesc = ptx::idesc_block_scaled(a_fmt, b_fmt, kBM, bn);
@@ -729,38 +765,37 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     g.rnd.keep = ~mask;
     g.rnd.even_on = (rounds && out_round == MXQ_ROUND_EVEN) ? 1u : 0u;
     g.rnd.add = !rounds ? 0u : (out_round == MXQ_ROUND_NEAREST ? (1u << (drop - 1)) : (out_round == MXQ_ROUND_EVEN ? (mask >> 1) : 0u));
-    g.bf16_exact = rounds && drop >= 16;
     g.epi_kind = (out_dtype == MXQ_BF16 && rounds && drop == 16 && !bias) ? out_round : 3;
     CUtensorMap ta, tb;
     int rc = make_operand_map(&ta, a_codes, batch, M, K, kBM);
     if (rc) return rc;
     rc = make_operand_map(&tb, b_codes, batch, N, K, bn);
     if (rc) return rc;
-    OutMaps tc;
     const int64_t es = out_dtype == MXQ_F32 ? 4 : 2;
     g.c_tma = (N * es) % 16 == 0;
     g.rows_per_dest = n_dests > 0 ? rows_per_dest : 0;
+    if (n_dests > 0 && !g.c_tma) return MXQ_ERR_UNSUPPORTED;          // destinations are written by TMA stores only
+    // Engine.  CTA pairs on 256 x 256 tiles when the problem gives every SM pair a tile and has a long
+    // K loop; otherwise single CTAs on 128 x 256 tiles (a short K loop makes the kernel store-bound:
+    // fewer operand stages, wide output boxes and a deeper staging ring), or 128 x 128 for narrow N.
+    const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256) * batch;
+    const bool pair = tiles2 >= sm_count() / 2 && M >= 256 && N >= 256 && K >= 1024 && g.c_tma;
+    const bool short_k = !pair && bn == 256 && K <= 512;
+    const int box_bytes = pair ? MXQ_PAIR_BOX : (short_k ? 128 : 64);
+    OutMaps tc;
     for (int d = 0; d < kMaxDests; ++d) tc.m[d] = ta;                  // placeholders, never dereferenced
     if (n_dests > 0) {
-        if (!g.c_tma) return MXQ_ERR_UNSUPPORTED;                      // destinations are written by TMA stores only
         for (int d = 0; d < n_dests; ++d) {
             const int64_t rows = std::min<int64_t>(rows_per_dest, M - d * rows_per_dest);   // the last one may be ragged
             if (rows <= 0) break;
-            rc = make_output_map(&tc.m[d], dests[d], 1, rows, N, out_dtype == MXQ_F32);
+            rc = make_output_map(&tc.m[d], dests[d], 1, rows, N, out_dtype == MXQ_F32, box_bytes);
             if (rc) return rc;
         }
     } else if (g.c_tma) {
-        rc = make_output_map(&tc.m[0], c, batch, M, N, out_dtype == MXQ_F32);
+        rc = make_output_map(&tc.m[0], c, batch, M, N, out_dtype == MXQ_F32, box_bytes);
         if (rc) return rc;
     }
-    // CTA pairs on 256 x 256 tiles when there is at least one tile per pair of SMs
-    static const int pair_mode = [] { const char* e = getenv("MXQ_GEMM_PAIR"); return e ? atoi(e) : 2; }();
-    const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256) * batch;
-    // MXQ_GEMM_PAIR: 0 = never, 1 = always, 2 (default) = for problems that fill every SM pair and
-    // have a long K loop (measured: +2..5 % there, slower for short K where the epilogue dominates)
-    const bool want_pair = pair_mode == 1 ||
-                           (pair_mode == 2 && tiles2 >= sm_count() / 2 && M >= 256 && N >= 256 && K >= 1024);
-    if (want_pair && g.c_tma) {
+    if (pair) {
         GemmArgs gp = g;
         gp.m_tiles = (M + 255) / 256;
         gp.n_tiles = (N + 255) / 256;
@@ -772,13 +807,11 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
         if (rc) return rc;
         rc = make_sf_map(&tsb, b_scales, batch, g.sfb_rows128, g.k_blocks);
         if (rc) return rc;
-        return launch_gemm_pair<6>(ta, tb2, tsa, tsb, tc, gp, (cudaStream_t)stream);
+        return launch_gemm_pair<MXQ_PAIR_STAGES, MXQ_PAIR_BOX, 1>(ta, tb2, tsa, tsb, tc, gp, (cudaStream_t)stream);
     }
-    // two 256-column accumulators (scale columns parked in the idle one); MXQ_GEMM_ACC2=0 selects one
-    static const int acc2 = [] { const char* e = getenv("MXQ_GEMM_ACC2"); return e ? atoi(e) : 1; }();
-    if (bn == 256 && acc2) return launch_gemm<256, 4, 2>(ta, tb, tc, g, (cudaStream_t)stream);
-    if (bn == 256) return launch_gemm<256, 4, 1>(ta, tb, tc, g, (cudaStream_t)stream);
-    return launch_gemm<128, 6, 2>(ta, tb, tc, g, (cudaStream_t)stream);
+    if (short_k) return launch_gemm<256, 3, 2, 128, 2>(ta, tb, tc, g, (cudaStream_t)stream);
+    if (bn == 256) return launch_gemm<256, 4, 2, 64, 1>(ta, tb, tc, g, (cudaStream_t)stream);
+    return launch_gemm<128, 6, 2, 64, 1>(ta, tb, tc, g, (cudaStream_t)stream);
 }
 }  // namespace mxq
 
@@ -815,11 +848,3 @@ extern "C" int mxq_device_status(int clear) {
     if (clear && v != 0) cudaMemset(w, 0, sizeof(int));
     return v;
 }
-
-#ifdef MXQ_GEMM_TRACE
-extern "C" int mxq_debug_read(long long* out, int n) {
-    int* w = mxq::device_status_word();
-    if (!w) return -1;
-    return cudaMemcpy(out, w + 16, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
-}
-#endif

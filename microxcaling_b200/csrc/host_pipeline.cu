@@ -7,7 +7,6 @@
 // needs a few percent of that time), so the pipeline's job is to keep both
 // directions of the link busy.
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 #include "mxq_common.cuh"
 
@@ -16,16 +15,7 @@ namespace mxq {
 constexpr int kPipeSlots = 3;
 constexpr int64_t kChunkBytes = int64_t(16) << 20;     // default target of input bytes per chunk
 
-// MXQ_HOST_CHUNK_MB (1..64) overrides the chunk size; the workspace is sized for the maximum.
-static int64_t chunk_bytes() {
-    static int64_t v = 0;
-    if (v == 0) {
-        const char* e = getenv("MXQ_HOST_CHUNK_MB");
-        const long mb = e ? atol(e) : 0;
-        v = (mb >= 1 && mb <= 64) ? (int64_t(mb) << 20) : kChunkBytes;
-    }
-    return v;
-}
+static constexpr int64_t chunk_bytes() { return kChunkBytes; }
 
 struct HostPipe {
     cudaStream_t s[kPipeSlots];

@@ -6,6 +6,7 @@
 // sequence mx/linear.py:62-96 performs on every forward call, minus the weight
 // quantization, which an inference caller does once.
 #include <algorithm>
+#include <mutex>
 #include "mxq_common.cuh"
 
 namespace mxq {
@@ -107,8 +108,10 @@ static __device__ __align__(256) unsigned char g_linear_scratch[kLinearStaticByt
 
 static void* linear_static_base(int* rc_out) {
     static void* base[64] = {nullptr};
+    static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *rc_out = MXQ_ERR_CUDA; return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
     if (!base[dev]) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_linear_scratch) != cudaSuccess || !p) { *rc_out = MXQ_ERR_CUDA; return nullptr; }

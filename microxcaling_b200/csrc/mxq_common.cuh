@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 #include "mxq_math.cuh"
 #include "../../include/mxq.h"
 
@@ -12,13 +13,18 @@ namespace mxq {
 // sized from the queried SM count, this is only the fallback.
 constexpr int kDefaultSMs = 148;
 
+// SM count of the current device, cached per device index.  The cache holds
+// plain ints written with the same value by every thread that races on a
+// first use, so it needs no lock.
 inline int sm_count() {
-    static int n = 0;
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kDefaultSMs;
+    int n = cache[dev].load(std::memory_order_relaxed);
     if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
             n = kDefaultSMs;
+        cache[dev].store(n, std::memory_order_relaxed);
     }
     return n;
 }

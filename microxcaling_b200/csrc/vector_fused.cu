@@ -14,6 +14,7 @@
 #include "vector_math.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
+#include <mutex>
 #include <math_constants.h>
 
 namespace mxq {
@@ -34,8 +35,10 @@ __global__ void build_table_kernel(uint16_t* tab) {
 template <int WHICH>
 static const uint16_t* bf16_table() {
     static uint16_t* tabs[64] = {nullptr};
+    static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
     if (!tabs[dev]) {
         uint16_t* t = nullptr;
         if (cudaMalloc(&t, 65536 * sizeof(uint16_t)) != cudaSuccess) { cudaGetLastError(); return nullptr; }

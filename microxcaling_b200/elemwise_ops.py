@@ -5,7 +5,9 @@ and the internal `_quantize_elemwise_core` (:82), `_quantize_elemwise` (:173),
 `_quantize_bfloat` (:191), `_quantize_fp` (:209).
 
 CUDA tensors always run the sm_100a kernel behind the C ABI (there is no eager
-path for them); CPU tensors use an exact float64 formulation in torch ops.
+path for them); CPU tensors use the library's host quantizer when `custom_cuda`
+is set (the chunked GPU pipeline when they are pinned) and an exact float64
+formulation in torch ops otherwise.
 """
 import torch
 
@@ -79,6 +81,13 @@ def _quantize_elemwise_core(A, bits, exp_bits, max_norm, round="nearest", satura
             and torch.cuda.is_available():
         from . import _backend
         return _backend.quantize_elemwise_host(A, bits, exp_bits, max_norm, _MODE[round], saturate_normals, allow_denorm)
+    if custom_cuda and bits <= 24 and A.dtype in (torch.float32, torch.float16, torch.bfloat16) and \
+            (round != "dither" or noise is not None):
+        # CPU tensor with custom_cuda: the library's host quantizer (the reference calls its C++ loop here,
+        # mx/elemwise_ops.py:122-124)
+        from . import _backend
+        return _backend.cpu_quantize_elemwise(A, bits, exp_bits, max_norm, _MODE[round], saturate_normals,
+                                              allow_denorm, noise)
     return _round_host(A, bits, exp_bits, max_norm, round, saturate_normals, allow_denorm, noise)
 
 

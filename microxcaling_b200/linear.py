@@ -21,7 +21,7 @@ torch_matmul = torch.matmul
 class LinearFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None,
-                inference=False):
+                packed_weight=None):
         bf_in = quantize_elemwise_op(input, mx_specs=mx_specs, round=mx_specs["round_output"])
         if prequantized_weights:
             assert weight.dtype == torch.bfloat16
@@ -44,8 +44,7 @@ class LinearFunction(torch.autograd.Function):
             bf_weight = bf_weight.to(bf_in.dtype)
         output = mx_gemm(bf_in, bf_weight, mx_specs["a_elem_format"], mx_specs["w_elem_format"], mx_specs,
                          mx_specs["round_mx_output"], mx_specs["round_mx_output"], mx_specs["round_output"],
-                         bias=bf_bias, trans2=True,
-                         in2_source=weight if inference else None)
+                         bias=bf_bias, trans2=True, in2_packed=packed_weight)
         ctx.mx_specs = get_backwards_mx_specs(mx_specs)
         ctx.prequantized_weights = prequantized_weights
         ctx.name = name
@@ -93,15 +92,14 @@ class LinearFunction(torch.autograd.Function):
         return (grad_input, grad_weight, grad_bias, None, None, None, None)
 
 
-def linear(input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None):
+def linear(input, weight, bias=None, mx_specs=None, prequantized_weights=False, name=None, packed_weight=None):
+    """`packed_weight`: a PackedMX of `weight` (w_elem_format, round_mx_output, blocks along in_features) made
+    once by the caller; the weight is then not quantized again in this call (inference only)."""
     mx_assert_test(mx_specs)
     if mx_specs is None:
         return f_linear(input, weight, bias=bias)
     mx_specs = apply_mx_specs(mx_specs)
-    # nothing will be differentiated: the packed weight may be kept for the next call
-    inference = not torch.is_grad_enabled() or not (input.requires_grad or weight.requires_grad or
-                                                    (bias is not None and bias.requires_grad))
-    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name, inference)
+    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name, packed_weight)
 
 
 class Linear(torch.nn.Linear):
@@ -110,6 +108,7 @@ class Linear(torch.nn.Linear):
         self.mx_none = mx_specs is None
         self.name = name
         self.prequantized_weights = False
+        self._packed = None                      # (key, PackedMX) of the frozen weight, see prequantize_weights
         self.mx_specs = apply_mx_specs(mx_specs)
         super().__init__(in_features, out_features, bias)
 
@@ -121,8 +120,26 @@ class Linear(torch.nn.Linear):
     def append_name(self, postfix):
         self.name += postfix
 
+    def packed_weight(self):
+        """The weight as a packed MX operand (w_elem_format, blocks of 32 along in_features), made on
+        first use after prequantize_weights() and kept while the parameter is the same storage at the
+        same version.  Writes that bypass the version counter (`weight.data.mul_()`) are not seen:
+        call prequantize_weights() again after such an update.  None when the tensor-core path does
+        not apply (CPU weights, fixed-point formats, block size other than 32)."""
+        from ._mxgemm import _fast_ok, _fmt, _pack
+        sp, w = self.mx_specs, self.weight
+        if not (w.is_cuda and _fast_ok(w, w, _fmt(sp["w_elem_format"]), _fmt(sp["w_elem_format"]), sp,
+                                       self.in_features, sp["round_mx_output"], sp["round_mx_output"],
+                                       sp["round_output"])):
+            return None
+        key = (w.data_ptr(), w._version, w.dtype, str(sp["w_elem_format"]), sp["round_mx_output"], sp["scale_bits"])
+        if self._packed is None or self._packed[0] != key:
+            self._packed = (key, _pack(w.detach(), _fmt(sp["w_elem_format"]), sp, sp["round_mx_output"], True))
+        return self._packed[1]
+
     def prequantize_weights(self):
-        """Store weight and bias as bfloat16 once (inference only)."""
+        """Store weight and bias as bfloat16 once (inference only); the forward pass then also keeps
+        the MX-packed weight instead of quantizing it in every call."""
         if self.mx_none:
             return
         assert self.mx_specs["round"] == "even", "Bfloat round should be 'even' for prequantizing weights."
@@ -137,11 +154,13 @@ class Linear(torch.nn.Linear):
                 self.bias.data = quantize_elemwise_op(self.bias.data, mx_specs=self.mx_specs,
                                                       round=self.mx_specs["round_weight"]).to(torch.bfloat16)
         self.prequantized_weights = True
+        self._packed = None
 
     def forward(self, inputs):
         if self.mx_none:
             return super().forward(inputs)
         if self.prequantized_weights:
             assert self.training is False, "Cannot use prequantized weights when training!"
+        packed = self.packed_weight() if self.prequantized_weights and inputs.is_cuda else None
         return linear(input=inputs, weight=self.weight, bias=self.bias, mx_specs=self.mx_specs,
-                      prequantized_weights=self.prequantized_weights, name=self.name)
+                      prequantized_weights=self.prequantized_weights, name=self.name, packed_weight=packed)

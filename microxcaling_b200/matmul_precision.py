@@ -1,8 +1,10 @@
 """Context manager kept for API compatibility with the reference's
 mx/matmul_precision.py:38-53.  There it switches torch's fp32 matmul to bf16
-inputs when both element formats fit bf16 exactly; here the MX GEMMs run on the
-block-scaled tensor cores and never consult this flag, so the manager only
-scopes the same global torch settings (restored on exit, also on exceptions)."""
+inputs when both element formats fit bf16 exactly.  Here products of FP formats
+with block size 32 run on the block-scaled tensor cores and never consult this
+flag; the remaining products (fixed-point formats, other block sizes) follow the
+reference's construction, a torch GEMM on fake-quantized values inside this
+manager.  The global torch settings are restored on exit, also on exceptions."""
 from contextlib import contextmanager
 
 import torch

@@ -20,8 +20,8 @@ its FFN admits without changing results beyond fp32 accumulation order:
     owns those tokens (mxq_gemm_mx_scatter), one small NCCL all-reduce orders
     the ranks, and each rank adds the slabs it received in rank order
     (mxq_sum_slabs_f32).  This is the default for two ranks; for more ranks the
-    NCCL reduce-scatter is faster (see _peer_access_ok) and is used unless
-    MXQ_TP_FUSED_SCATTER=1.
+    NCCL reduce-scatter is faster (see _local_scatter_eligible) and is used unless
+    MXQ_TP_FUSED_SCATTER=1.  The ranks agree on the branch collectively.
 
 On CUDA tensors the GEMMs run on packed operands through libmxq; on CPU tensors
 (used by the gloo tests of this logic) the same steps run on fake-quantized
@@ -93,17 +93,16 @@ class _PeerSlabs:
             self.local = None
 
 
-def _peer_access_ok(device, world):
-    # Measured on B200 / NVSwitch (config-5 FFN forward): 2 GPUs 5.36 ms with the scattering GEMM vs 5.84 ms
-    # with the NCCL reduce-scatter; 8 GPUs 3.20 ms vs 2.28 ms -- with seven of eight tiles leaving over NVLink
-    # as 64-byte row segments the links are used at well under half their rate, so the scattering GEMM is the
-    # default only for two ranks.  MXQ_TP_FUSED_SCATTER=1 forces it, =0 forbids it.
+def _local_scatter_eligible(device, world):
+    """This rank's own view: may the scattering GEMM be used?  (The ranks then agree on the
+    minimum over all views, see TensorParallelFFN._use_scatter.)
+    Measured on B200 / NVSwitch (config-5 FFN forward) the scattering GEMM wins for two ranks and
+    loses to the NCCL reduce-scatter beyond that, so it is the default only for two ranks;
+    MXQ_TP_FUSED_SCATTER=1 asks for it at any size, =0 forbids it."""
     mode = os.environ.get("MXQ_TP_FUSED_SCATTER", "")
     if mode == "0" or world > 8 or (mode != "1" and world > 2):
         return False
-    me = device.index if device.index is not None else torch.cuda.current_device()
-    n = torch.cuda.device_count()
-    return n >= world and all(d == me or torch.cuda.can_device_access_peer(me, d) for d in range(world))
+    return device.type == "cuda"
 
 
 class TensorParallelFFN(torch.nn.Module):
@@ -121,9 +120,30 @@ class TensorParallelFFN(torch.nn.Module):
         self.w_gate = torch.nn.Parameter(torch.empty(hi - lo, hidden, **kw))
         self.w_up = torch.nn.Parameter(torch.empty(hi - lo, hidden, **kw))
         self.w_down = torch.nn.Parameter(torch.empty(hidden, hi - lo, **kw))
-        self._packed = None
+        self._packed = None                     # (key, packed weights), see _weights_packed
         self._slabs = None
-        self._no_peer = False
+        self._scatter = None                    # agreed by all ranks on the first multi-rank forward
+
+    def _use_scatter(self, device):
+        """Collective, once: every rank must take the same branch (scattering GEMM or NCCL
+        reduce-scatter), or the collectives of the two branches would be mismatched.  Each rank
+        contributes its own eligibility and its real device index; the answer is the minimum over
+        ranks, with peer access checked between the devices the ranks really run on."""
+        if self._scatter is None:
+            mine = _local_scatter_eligible(device, self.world)
+            idx = device.index if device.index is not None else (torch.cuda.current_device() if device.type == "cuda" else -1)
+            info = [None] * self.world
+            dist.all_gather_object(info, (bool(mine), int(idx)), group=self.group)
+            ok = all(e for e, _ in info)
+            if ok:
+                devs = [d for _, d in info]
+                ok = len(set(devs)) == self.world and all(
+                    d == idx or (0 <= d < torch.cuda.device_count() and torch.cuda.can_device_access_peer(idx, d))
+                    for d in devs)
+            flag = torch.tensor([1.0 if ok else 0.0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            self._scatter = float(flag.item()) >= 1.0
+        return self._scatter
 
     def _make_slabs(self, rows, device):
         """Collective: either every rank ends up with mapped receive buffers or none does (then the
@@ -135,7 +155,7 @@ class TensorParallelFFN(torch.nn.Module):
             slabs.close()
             dist.barrier(group=self.group)
             slabs.free()
-            self._no_peer = True
+            self._scatter = False
             return None
         return slabs
 
@@ -168,13 +188,21 @@ class TensorParallelFFN(torch.nn.Module):
             (self.cols[1] - self.cols[0]) % 128 == 0
 
     def _weights_packed(self):
-        if self._packed is None:
+        """The three weight shards as packed MX operands, remade when a parameter's storage or version
+        counter changes (an optimizer step, load_state_dict, load_full).  Writes that bypass the
+        version counter (`w.data.mul_()`) are not seen: call invalidate_packed_weights() after them."""
+        ws = (self.w_gate, self.w_up, self.w_down)
+        key = tuple((w.data_ptr(), w._version) for w in ws)
+        if self._packed is None or self._packed[0] != key:
             sp = self.mx_specs
             rnd = sp["round_mx_output"]
             wf = _fmt(sp["w_elem_format"])
             q = lambda w: _pack(quantize_elemwise_op(w.detach(), sp, round=sp["round_weight"]), wf, sp, rnd, True)
-            self._packed = (q(self.w_gate), q(self.w_up), q(self.w_down))
-        return self._packed
+            self._packed = (key, tuple(q(w) for w in ws))
+        return self._packed[1]
+
+    def invalidate_packed_weights(self):
+        self._packed = None
 
     def _all_gather_rows(self, t):
         if self.world == 1:
@@ -211,16 +239,17 @@ class TensorParallelFFN(torch.nn.Module):
         af = _fmt(sp["a_elem_format"])
         rnd, out_rnd = sp["round_mx_output"], _MODE[sp["round_output"]]
         bits = sp["bfloat"] if sp["bfloat"] >= 10 else 0
-        (gc, gs, gk), (uc, us, uk), (dc, ds, dk) = self._weights_packed()
+        pg, pu, pd = self._weights_packed()
         h = quantize_elemwise_op(h, sp, round=sp["round_output"])
-        xc, xs, xk = _pack(h, af, sp, rnd, True)                       # local tokens
-        xc, xs = self._all_gather_rows(xc), self._all_gather_rows(xs.view(-1, 512)).view(-1)
+        px = _pack(h, af, sp, rnd, True)                               # local tokens
+        xc, xs, xk = self._all_gather_rows(px.codes.reshape(-1, self.hidden)), \
+            self._all_gather_rows(px.scales.view(-1, 512)).view(-1), px.container
         T = xc.shape[0]
         Il = self.cols[1] - self.cols[0]
-        gate = be.gemm_mx(xc, xs, gc, gs, 1, T, Il, self.hidden, xk, gk, out_dtype=h.dtype, bfloat_bits=bits,
-                          round_mode=out_rnd)[0]
-        up = be.gemm_mx(xc, xs, uc, us, 1, T, Il, self.hidden, xk, uk, out_dtype=h.dtype, bfloat_bits=bits,
-                        round_mode=out_rnd)[0]
+        gate = be.gemm_mx(xc, xs, pg.codes, pg.scales, 1, T, Il, self.hidden, xk, pg.container, out_dtype=h.dtype,
+                          bfloat_bits=bits, round_mode=out_rnd)[0]
+        up = be.gemm_mx(xc, xs, pu.codes, pu.scales, 1, T, Il, self.hidden, xk, pu.container, out_dtype=h.dtype,
+                        bfloat_bits=bits, round_mode=out_rnd)[0]
         if fused_bf16_ok(sp, gate, up) and Il % 32 == 0 and sp["round_output"] in ("nearest", "floor", "even"):
             # SiLU(gate) * up and the MX packing of the product in one pass; the vector format leaves
             # bfloat16 values untouched, so the rounding between the two steps is the identity
@@ -231,12 +260,14 @@ class TensorParallelFFN(torch.nn.Module):
         else:
             act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
             act = quantize_elemwise_op(act, sp, round=sp["round_output"])
-            ac, as_, ak = _pack(act, af, sp, rnd, True)
+            pa = _pack(act, af, sp, rnd, True)
+            ac, as_, ak = pa.codes, pa.scales, pa.container
+        dc, ds, dk = pd.codes, pd.scales, pd.container
         if self.world == 1:
             return be.gemm_mx(ac, as_, dc, ds, 1, T, self.hidden, Il, ak, dk, out_dtype=h.dtype, bfloat_bits=bits,
                               round_mode=out_rnd)[0]
         rows = T // self.world
-        if self._slabs is None and not self._no_peer and _peer_access_ok(h.device, self.world):
+        if self._slabs is None and self._use_scatter(h.device):
             self._slabs = self._make_slabs(rows, h.device)
         sl = self._slabs
         if sl is not None and (sl.rows, sl.cols) == (rows, self.hidden):

@@ -40,8 +40,14 @@ def build(force=False):
             os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "mxq_oracle.c")):
         subprocess.check_call(["make", "-C", _HERE, "libmxq_oracle.so"],
                               stdout=subprocess.DEVNULL)
-    subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL,
-                    stderr=subprocess.DEVNULL)
+    ref_src = os.environ.get("MXQ_REFERENCE_DIR", "")
+    if not ref_src:
+        # the conventional place of the reference checkout beside this repository's parent
+        cand = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+        ref_src = cand if os.path.isfile(os.path.join(cand, "mx", "cpp", "funcs.h")) else ""
+    if ref_src:
+        subprocess.call(["make", "-C", _HERE, "ref", "REF=" + ref_src], stdout=subprocess.DEVNULL,
+                        stderr=subprocess.DEVNULL)
 
 
 def lib():

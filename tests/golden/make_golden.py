@@ -86,7 +86,7 @@ def recipe_for(x):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of a checkout of microsoft/microxcaling")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     sys.dont_write_bytecode = True

@@ -133,11 +133,14 @@ def test_attention_shaped_bmm_softmax_bmm():
     close_bf16(o_gpu, o_cpu.numpy(), "out")
 
 
-def test_packed_weight_is_reused_only_while_unchanged(monkeypatch):
-    """Inference calls reuse the packed weight of mx.Linear; an in-place update of the weight, a different
-    format, or autograd being on makes the layer pack it again."""
-    from microxcaling_b200 import _backend, _mxgemm
-    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16})
+def test_weight_is_requantized_every_call_unless_frozen(monkeypatch, tmp_path):
+    """Like the reference, mx.Linear quantizes its weight in every forward call, so an in-place update
+    through `.data` (which moves neither the pointer nor the version counter) is seen at once.  After
+    prequantize_weights() the packed weight is kept and reused; it can be saved and loaded."""
+    from microxcaling_b200 import _backend
+    from microxcaling_b200.packed import PackedMX
+    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16,
+                            "round": "even"})
     lin = mx.Linear(256, 128, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
     x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
     calls = []
@@ -145,17 +148,34 @@ def test_packed_weight_is_reused_only_while_unchanged(monkeypatch):
     monkeypatch.setattr(_backend, "quantize_mx", lambda A, *a, **k: (calls.append(tuple(A.shape)), real(A, *a, **k))[1])
     with torch.no_grad():
         y1 = lin(x)
-        n1 = len(calls)
+        lin.weight.data.mul_(2.0)                   # invisible to data_ptr / _version
+        n = len(calls)
         y2 = lin(x)
-        assert len(calls) - n1 == 1                 # only the activations were packed again
-        assert torch.equal(y1, y2)
-        lin.weight.mul_(2.0)
-        n2 = len(calls)
+        assert len(calls) - n == 2                  # activations and weight packed again
+        assert torch.equal(y2.float(), 2.0 * y1.float())
+        lin.eval()
+        lin.prequantize_weights()
         y3 = lin(x)
-        assert len(calls) - n2 == 2 and not torch.equal(y3, y1)
-    n3 = len(calls)
-    lin(x)                                          # autograd on: no reuse
-    assert len(calls) - n3 == 2
+        n = len(calls)
+        y4 = lin(x)
+        assert len(calls) - n == 1                  # only the activations
+        assert torch.equal(y3, y4) and torch.equal(y3, y2)
+        lin.weight.mul_(0.5)                        # a tracked in-place update: the packed weight follows
+        n = len(calls)
+        y5 = lin(x)
+        assert len(calls) - n == 2 and torch.equal(y5, y1)
+        # file round trip of the packed weight, used in place of the tensor
+        pw = lin.packed_weight()
+        path = str(tmp_path / "w.mxq")
+        pw.save(path)
+        back = PackedMX.load(path, device="cuda")
+        assert torch.equal(back.codes, pw.codes) and torch.equal(back.scales, pw.scales)
+        y6 = mx.linear(x, lin.weight, None, mx_specs=sp, prequantized_weights=True, packed_weight=back)
+        assert torch.equal(y6, y5)
+        # and its decoded values are the fake-quantized weight
+        from microxcaling_b200.mx_ops import quantize_mx_op
+        wq = quantize_mx_op(lin.weight.detach(), sp, elem_format="fp8_e4m3", axes=[-1], round=sp["round_mx_output"])
+        assert torch.equal(back.dequantize(torch.float32)[0], wq.float())
 
 
 def test_linear_with_odd_feature_count_takes_the_tensor_core_path(monkeypatch):

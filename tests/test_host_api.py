@@ -146,3 +146,95 @@ def test_dither_is_reproducible_with_given_noise():
     assert torch.equal(a, b)
     q = (a - lo).abs()
     assert (q >= 0).all() and ((a.abs() >= lo.abs()) | (a == lo)).all()
+
+
+def test_cpu_twins_match_recorded_reference(golden_recorded):
+    """mxq_cpu_quantize_mx / mxq_cpu_quantize_elemwise (the host C++ quantizers behind
+    funcs.quantize_mx_func_cpp / quantize_elemwise_func_cpp) against every call recorded from the
+    reference's own CPU test-suite."""
+    from microxcaling_b200 import _backend as be
+    meta, z = golden_recorded
+    bad = []
+    for i, rec in enumerate(meta):
+        if "recipe" in rec:
+            e, m, inf = rec["recipe"]
+            x = all_encodings(e, m, bool(inf)).reshape(rec["shape"])
+        else:
+            x = z["x%d" % i]
+        if x.ndim == 0:
+            continue
+        p = rec["params"]
+        t = torch.as_tensor(x)
+        if rec["kind"] == "mx":
+            eb, mb, mn = oracle.FORMATS[p["fmt"]]
+            y = be.cpu_quantize_mx(t, p["scale_bits"], eb, mb, mn, p["block"], p["axis"], p["flush"],
+                                   oracle.ROUND[p["round"]]).numpy()
+        else:
+            y = be.cpu_quantize_elemwise(t, p["bits"], p["exp_bits"], p["max_norm"], oracle.ROUND[p["round"]],
+                                         p["saturate"], p["allow_denorm"]).numpy()
+        ok = (sha(y) == rec["sha"]) if "sha" in rec else oracle.same_values(y, z["y%d" % i])
+        if not ok:
+            bad.append((i, rec["kind"], p))
+    assert not bad, bad[:5]
+
+
+def test_cpu_twins_storage_types_and_legacy_names():
+    """fp16 / bf16 host tensors, the dispatch of custom_cuda=True on CPU tensors, the seven legacy names."""
+    from microxcaling_b200 import _backend as be
+    torch.manual_seed(1)
+    x = torch.randn(33, 96) * torch.exp2(torch.randint(-20, 20, (33, 96)).float())
+    for dt in (torch.float16, torch.bfloat16):
+        xd = x.to(dt)
+        for fmt in ("fp8_e4m3", "fp4_e2m1", "int8"):
+            eb, mb, mn = oracle.FORMATS[fmt]
+            for axis in (0, 1):
+                y = be.cpu_quantize_mx(xd, 8, eb, mb, mn, 32, axis)
+                want = oracle.quantize_mx(xd.float().numpy(), fmt, axis=axis)
+                assert y.dtype == dt
+                assert oracle.same_values(y.float().numpy(), torch.as_tensor(want).to(dt).float().numpy()), (dt, fmt, axis)
+        y = be.cpu_quantize_elemwise(xd, 5, 8, 2.0 ** 127 * 1.75, 2)
+        want = oracle.quantize_elemwise(xd.float().numpy(), 5, 8, 2.0 ** 127 * 1.75, "even")
+        assert oracle.same_values(y.float().numpy(), torch.as_tensor(want).to(dt).float().numpy())
+    # fp32 in, bf16 out, round-even = torch's cast
+    y = be.cpu_quantize_elemwise(x, 9, 8, 3.3895313892515355e38, 2, out_dtype=torch.bfloat16)
+    assert torch.equal(y, x.to(torch.bfloat16))
+    # custom_cuda=True on an ordinary CPU tensor reaches the host quantizer and equals the torch formulation
+    a = _quantize_mx(x, 8, "fp6_e3m2", axes=[0], block_size=32, custom_cuda=True)
+    b = _quantize_mx(x, 8, "fp6_e3m2", axes=[0], block_size=32, custom_cuda=False)
+    assert oracle.same_values(a.numpy(), b.numpy())
+    a = _quantize_elemwise_core(x, 7, 5, 57344.0, "nearest", custom_cuda=True)
+    b = _quantize_elemwise_core(x, 7, 5, 57344.0, "nearest", custom_cuda=False)
+    assert oracle.same_values(a.numpy(), b.numpy())
+    # the reference's call pattern: blocks reshaped onto their own axis, that whole axis shared
+    xb = x[:32].reshape(1, 32, 96)
+    mv = xb.abs().max(dim=1, keepdim=True).values
+    y = be.funcs.quantize_mx_func_cpp(xb, 8, 4, 5, 448.0, mv, 1, False, 0)
+    assert oracle.same_values(y.reshape(32, 96).numpy(), oracle.quantize_mx(x[:32].numpy(), "fp8_e4m3", axis=0))
+    y = be.funcs.quantize_elemwise_func_cpp(x, 9, 8, 3.3895313892515355e38, 0, False, True)
+    assert oracle.same_values(y.numpy(), oracle.quantize_elemwise(x.numpy(), 9, 8, 3.3895313892515355e38))
+    with pytest.raises(be.MxqError):
+        be.funcs.quantize_mx_func_cpp(torch.zeros(1, 1, 1, 1, 1, 2), 8, 4, 5, 448.0, None, 1)
+    # dither with a caller noise tensor: host quantizer == torch formulation
+    n = torch.rand_like(x)
+    a = _quantize_mx(x, 8, "fp6_e2m3", axes=[-1], block_size=32, round="dither", noise=n, custom_cuda=True)
+    b = _quantize_mx(x, 8, "fp6_e2m3", axes=[-1], block_size=32, round="dither", noise=n, custom_cuda=False)
+    assert oracle.same_values(a.numpy(), b.numpy())
+
+
+def test_shared_exp_method_none_and_block_helpers():
+    """shared_exp_method='none' (an exponent per value) = blocks of one element; the block
+    helpers keep the reference's contract (mx/mx_ops.py:49-170)."""
+    from microxcaling_b200.mx_ops import _reshape_to_blocks, _undo_reshape_to_blocks, _shared_exponents
+    torch.manual_seed(2)
+    x = torch.randn(6, 40)
+    y = _quantize_mx(x, 8, "fp4_e2m1", shared_exp_method="none", axes=[-1], block_size=32)
+    assert oracle.same_values(y.numpy(), oracle.quantize_mx(x.numpy(), "fp4_e2m1", axis=1, block=1))
+    with pytest.raises(Exception):
+        _quantize_mx(x, 8, "fp4_e2m1", shared_exp_method="mean", axes=[-1], block_size=32)
+    b, axes, orig, padded = _reshape_to_blocks(x, [-1], 32)
+    assert tuple(b.shape) == (6, 2, 32) and axes == [1] and tuple(orig) == (6, 40, 1) and tuple(padded) == (6, 64, 1)
+    assert torch.equal(_undo_reshape_to_blocks(b, padded, orig, axes), x)
+    e = _shared_exponents(b, "max", [2])
+    assert tuple(e.shape) == (6, 2, 1)
+    assert torch.equal(e[:, 0, 0], torch.floor(torch.log2(x[:, :32].abs().max(dim=1).values)))
+    assert float(_shared_exponents(torch.zeros(4), "max", [0])) == -126.0
