@@ -213,6 +213,25 @@ int mxq_swiglu_quantize_mx(const void* gate, const void* up, void* codes, void* 
                            int flush_fp32_subnorms, int rmode, int flags, int64_t sf_rows_per_batch, void* stream);
 
 /*
+ * Softmax over the last dimension (the chain of mxq_softmax_bf16, exp only)
+ * fused into the MX packing of the probabilities along that dimension: what
+ * mxq_softmax_bf16 followed by mxq_quantize_mx (codes + scales) writes, with the
+ * score matrix read once and the probabilities never re-read.  Replaces, in an
+ * attention block, SoftmaxFunction.forward (mx/softmax.py:18-41) and the
+ * quantize_mx_op of the left operand of the product that follows
+ * (mx/bmm.py:40-59, mx/matmul.py:68-86).
+ *   x       bfloat16 [rows, cols], cols % 32 == 0, cols <= 2048
+ *   probs   bfloat16 [rows, cols] or NULL (the caller does not need them)
+ *   codes, scales, element format, rmode, flags, sf_rows_per_batch
+ *           as in mxq_swiglu_quantize_mx (block 32, nearest / floor / even)
+ * Reads exp from the table mxq_softmax_bf16 describes (built by the first call
+ * on a device: make that call outside stream capture).
+ */
+int mxq_softmax_quantize_mx(const void* x, void* probs, void* codes, void* scales, int64_t rows, int64_t cols,
+                            int scale_bits, int elem_ebits, int elem_mbits, float elem_max_norm,
+                            int flush_fp32_subnorms, int rmode, int flags, int64_t sf_rows_per_batch, void* stream);
+
+/*
  * Block-scaled MX GEMM on the tensor cores (tcgen05 kind::mxf8f6f4):
  *   C[b] = A[b] (M x K) * B[b]^T (N x K),  b < batch, fp32 accumulation.
  * Takes the place of the library GEMM the reference runs on dequantized
@@ -302,8 +321,12 @@ int64_t mxq_linear_workspace_bytes(int64_t M, int64_t K);
  *     overlap on the GPU (different streams) race on it; calls on one stream
  *     are ordered and safe.  The array keeps the last call's contents; each
  *     call re-zeroes the parts it relies on (status word, scale region).
- *   - mxq_linear_static_status() reads the status word of the last call
- *     (synchronous): 0, or MXQ_ERR_DEVICE if a kernel gave up on a wait.
+ *   - The array is the CURRENT device's: x, y and the weight must live on the
+ *     current device (MXQ_ERR_BAD_ARG otherwise; nothing is launched).
+ *   - mxq_linear_static_status() reads the status word of the last call on the
+ *     current device: 0, or MXQ_ERR_DEVICE if a kernel gave up on a wait.  It
+ *     copies with a blocking cudaMemcpy, which does not wait for work on
+ *     non-blocking streams: synchronize the stream the call was made on first.
  */
 int mxq_linear_fwd_static(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits, int a_mbits,
                           float a_max_norm, int a_round, int scale_bits, int flush_fp32_subnorms,
@@ -312,8 +335,10 @@ int mxq_linear_fwd_static(const void* x, int x_dtype, int64_t M, int64_t K, int 
 int64_t mxq_linear_static_max_elems(void);
 int mxq_linear_static_status(void);
 
-/* Synchronously reads (and optionally clears) the current device's status word:
- * 0, or MXQ_ERR_DEVICE after a kernel timed out on a wait. */
+/* Reads (and optionally clears) the current device's status word: 0, or
+ * MXQ_ERR_DEVICE after a kernel timed out on a wait.  The read is a blocking
+ * cudaMemcpy, which does not wait for work on non-blocking streams:
+ * synchronize the streams the GEMMs ran on first. */
 int mxq_device_status(int clear);
 
 #ifdef __cplusplus

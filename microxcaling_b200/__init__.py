@@ -12,3 +12,4 @@ from .activations import SiLU, silu  # noqa: F401
 from .layernorm import RMSNorm  # noqa: F401
 from .simd_ops import simd_add, simd_sub, simd_mul, simd_div  # noqa: F401
 from .softmax import Softmax, softmax  # noqa: F401
+from .convolution import Conv1d, Conv2d, Conv3d, ConvTranspose2d, conv1d, conv2d, conv3d, conv_transpose2d  # noqa: F401

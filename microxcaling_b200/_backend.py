@@ -57,6 +57,7 @@ def lib():
         L.mxq_silu_bf16.argtypes = [vp, vp, vp, vp, i64, vp]
         L.mxq_softmax_bf16.argtypes = [vp, vp, i64, i64, i32, vp]
         L.mxq_swiglu_quantize_mx.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, f32, i32, i32, i32, i64, vp]
+        L.mxq_softmax_quantize_mx.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, f32, i32, i32, i32, i64, vp]
         L.mxq_gemm_mx_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i32, i32, i32,
                                           i32, i32, i32, vp]
         L.mxq_sum_slabs_f32.argtypes = [vp, i32, i64, vp, vp]
@@ -441,6 +442,26 @@ def softmax_bf16(x, use_exp2=False):
         check(lib().mxq_softmax_bf16(_ptr(x), _ptr(out), x.numel() // cols if cols else 0, cols, int(bool(use_exp2)),
                                      _stream(x)))
     return out
+
+
+def softmax_quantize_mx(x, scale_bits, ebits, mbits, max_norm, flush=False, rmode=0, rows_per_batch=0,
+                        want_probs=True):
+    """Softmax over the last dimension of bfloat16 x fused with the MX packing of the probabilities;
+    see mxq_softmax_quantize_mx.  Returns (probs or None, codes uint8 like x, scales uint8 in the GEMM layout)."""
+    _require_bf16(x, "x")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    rpb = rows_per_batch or rows
+    probs = torch.empty_like(x) if want_probs else None
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    nb = rows // rpb if rpb else 0
+    alloc = torch.empty if rpb % 128 == 0 and cols % 128 == 0 else torch.zeros
+    scales = alloc(nb * ((rpb + 127) // 128) * ((cols + 127) // 128) * 512, dtype=torch.uint8, device=x.device)
+    with _device_of(x.device):
+        check(lib().mxq_softmax_quantize_mx(_ptr(x), _ptr(probs), _ptr(codes), _ptr(scales), rows, cols, int(scale_bits),
+                                            int(ebits), int(mbits), float(max_norm), int(bool(flush)), int(rmode),
+                                            SCALES_GEMM_LAYOUT, int(rpb), _stream(x)))
+    return probs, codes, scales
 
 
 def rmsnorm_bf16(x, weight, bias, eps, want_saved=False):

@@ -15,7 +15,7 @@ from .elemwise_ops import quantize_elemwise_op
 from .formats import ElemFormat, _get_format_params
 from .matmul_precision import set_matmul_precision
 from .mx_ops import quantize_mx_op
-from .packed import PackedMX
+from .packed import PackedMX, packed_note
 
 _MODE = {"nearest": 0, "floor": 1, "even": 2}
 _torch_matmul = torch.matmul
@@ -76,6 +76,11 @@ def mx_gemm(in1, in2, fmt1, fmt2, specs, round1, round2, out_round, bias=None, t
         else:
             batch, rows = (in1.numel() // (M * K)), M
         a = in1_packed
+        if a is None and not trans1:
+            # probabilities packed by the fused softmax carry their packing along
+            a = packed_note(in1, fmt1, round1, specs)
+            if a is not None and shared_b and a.rows % 128 != 0:
+                a = None                        # scale chunks were laid out per batch element
         if a is None:
             # with a shared right operand the scales are laid out for all rows in one batch element
             a = _pack(in1.reshape(-1, K) if shared_b else in1, fmt1, specs, round1, not trans1)

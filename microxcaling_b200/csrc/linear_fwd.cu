@@ -6,6 +6,7 @@
 // sequence mx/linear.py:62-96 performs on every forward call, minus the weight
 // quantization, which an inference caller does once.
 #include <algorithm>
+#include <initializer_list>
 #include <mutex>
 #include "mxq_common.cuh"
 
@@ -137,6 +138,15 @@ extern "C" int mxq_linear_fwd_static(const void* x, int x_dtype, int64_t M, int6
     if (m_pad > kLinearStaticMaxElems / K) return MXQ_ERR_TOO_LARGE;   // ceil(M/128)*128*K beyond the fixed array
     void* base = linear_static_base(&rc);
     if (!base) return rc;
+    // The array belongs to the CURRENT device.  A caller whose current device is not the one x and y live
+    // on would hand the kernels another GPU's address: refuse that instead of launching.
+    int cur = -1;
+    cudaPointerAttributes pa;
+    if (cudaGetDevice(&cur) != cudaSuccess) return MXQ_ERR_CUDA;
+    for (const void* p : {x, (const void*)y, w_codes}) {
+        if (cudaPointerGetAttributes(&pa, p) != cudaSuccess) { cudaGetLastError(); return MXQ_ERR_CUDA; }
+        if (pa.type == cudaMemoryTypeDevice && pa.device != cur) return MXQ_ERR_BAD_ARG;
+    }
     // The array still holds the previous call's packed activations; linear_fwd_impl zeroes the
     // status word and the scale region (its padding rows are read but never written) before use.
     return linear_fwd_impl(x, x_dtype, M, K, a_ebits, a_mbits, a_max_norm, a_round, scale_bits, flush_fp32_subnorms,

@@ -67,6 +67,7 @@ struct MxArgs {
     uint32_t fp_cmin_base;         // bits of cmin   = fp_cmin_base + (E << 23)
     uint32_t fp_maxn_base;         // bits of maxn   = fp_maxn_base + (E << 23)
     uint32_t fp_mp_base;           // packed bf16 maxn pair = fp_mp_base + E * 0x00800080
+    int direct8;                   // element format IS the code container (fp8_e4m3 / fp8_e5m2): see code_pair_direct
 };
 
 // The unscaled fast path needs its per-block constants to be normal, finite
@@ -90,6 +91,8 @@ __host__ inline void set_fast_consts(MxArgs& a) {
     a.fp_cmin_base = ((uint32_t)(emin_f + kf_f) << 23) - (127u << 23);
     a.fp_maxn_base = mn - (127u << 23);
     a.fp_mp_base = (uint32_t)(mp_half < 0 ? 0 : mp_half) * 0x10001u;
+    a.direct8 = (a.fmt.ebits == 4 && a.fmt.mbits == 5 && a.fmt.max_norm == 448.0f) ||
+                (a.fmt.ebits == 5 && a.fmt.mbits == 4 && a.fmt.max_norm == 57344.0f);
 }
 
 // Last-axis kernels: byte index of the scale of linear block index `blk`
@@ -414,6 +417,28 @@ __device__ __forceinline__ uint32_t code_quad(float q0, float q1, float q2, floa
     return __byte_perm(lo, hi, 0x5410) | (__byte_perm(w01, w23, 0x7531) & 0x80808080u);
 }
 
+// Codes straight from the hardware conversion, for the two formats that ARE their container (fp8_e4m3,
+// fp8_e5m2) when only the packed operand is wanted: cvt.rn.satfinite rounds the scaled value to the
+// format's grid (subnormals included) to nearest-even and saturates at max_norm, which is the element
+// rounding of MX in 'even' mode; for 'nearest' (ties away from zero) the scale factor carries a relative
+// nudge of 2^-12, which turns every exact tie into a round-up and moves nothing else (a bfloat16 source
+// has 8 significant bits, so x / spacing is never within 2^-8 of a half-way point without being on it).
+// c = 2^-s (exact reciprocal of the block scale) or 2^-s * (1 + 2^-12); the products are exact in fp32
+// (8 x 13 significant bits).  The sign travels through the conversion.  Two pairs -> four code bytes.
+template <int CK>
+__device__ __forceinline__ uint32_t code_quad_direct(uint32_t w01, uint32_t w23, float c0, float c1, float c2, float c3) {
+    const float v0 = __uint_as_float(w01 << 16) * c0, v1 = __uint_as_float(w01 & 0xffff0000u) * c1;
+    const float v2 = __uint_as_float(w23 << 16) * c2, v3 = __uint_as_float(w23 & 0xffff0000u) * c3;
+    const uint32_t lo = CK == CK_E5M2 ? encode2_e5m2(v0, v1) : encode2_e4m3(v0, v1);
+    const uint32_t hi = CK == CK_E5M2 ? encode2_e5m2(v2, v3) : encode2_e4m3(v2, v3);
+    return __byte_perm(lo, hi, 0x5410);
+}
+// the factor c of a block: bits of 2^-s with the 2^-12 nudge in the mantissa for half-away rounding
+template <int MODE>
+__device__ __forceinline__ float direct_factor(float inv) {
+    return MODE == RN_AWAY ? __uint_as_float(__float_as_uint(inv) | 0x800u) : inv;
+}
+
 // code-byte sinks of the slow path
 struct StridedBytes {                    // global memory, element r at p[r * s]
     uint8_t* p;
@@ -541,6 +566,14 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
             } else if (live[u]) {
                 bf16_block_slow<MODE, CK>(a, reinterpret_cast<const uint16_t*>(a.in), v * 8, 1, 8, m << 16,
                                           StridedBytes{CK != CK_NONE ? a.codes + v * 8 : nullptr, 1}, 8);
+            }
+            continue;
+        }
+        if (!WANT_DQ && CK != CK_NONE && MODE != RZ && a.direct8) {
+            if (live[u]) {
+                const float cf = direct_factor<MODE>(fb.inv);
+                reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(code_quad_direct<CK>(w[0], w[1], cf, cf, cf, cf),
+                                                                   code_quad_direct<CK>(w[2], w[3], cf, cf, cf, cf));
             }
             continue;
         }
@@ -685,7 +718,12 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             } else {
                 const uint32_t mp0 = a.fp_mp_base + ((fb[0].E | (fb[1].E << 16)) << 7);
                 const uint32_t mp1 = a.fp_mp_base + ((fb[2].E | (fb[3].E << 16)) << 7);
-                const float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
+                const bool direct = !WANT_DQ && CK != CK_NONE && MODE != RZ && a.direct8;
+                float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
+                if (direct) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) inv[i] = direct_factor<MODE>(inv[i]);
+                }
                 uint32_t tc[4][4];                 // transposed codes: [column][4 rows per word], 16 rows
 #pragma unroll
                 for (int r4 = 0; r4 < kMaxRows / 4; ++r4) {
@@ -693,6 +731,12 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
 #pragma unroll
                     for (int rr = 0; rr < 4; ++rr) {
                         const int r = r4 * 4 + rr;
+                        if (!WANT_DQ && CK != CK_NONE && MODE != RZ && direct) {
+                            c4[rr] = code_quad_direct<CK>(raw[r].x, raw[r].y, inv[0], inv[1], inv[2], inv[3]);
+                            if (!TRANSPOSED)
+                                *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c4[rr];
+                            continue;
+                        }
                         float q[4];
                         const uint32_t o0 = quant_pair_bf16<MODE, false>(raw[r].x, fb[0].cmin, fb[1].cmin, mp0, a.fmt, q[0], q[1]);
                         const uint32_t o1 = quant_pair_bf16<MODE, false>(raw[r].y, fb[2].cmin, fb[3].cmin, mp1, a.fmt, q[2], q[3]);

@@ -50,6 +50,8 @@ static const uint16_t* bf16_table() {
 }
 
 const uint16_t* sigmoid_table() { return bf16_table<0>(); }
+const uint16_t* exp_table() { return bf16_table<1>(); }
+int softmax_rows_large(const void* x, void* out, int64_t rows, int64_t cols, cudaStream_t st);
 
 constexpr int kVecThreads = 256;
 
@@ -396,14 +398,9 @@ extern "C" int mxq_softmax_bf16(const void* x, void* out, int64_t rows, int64_t 
     const uint16_t* xs = (const uint16_t*)x;
     uint16_t* os = (uint16_t*)out;
     if (!use_exp2 && rows * cols >= ((int64_t)1 << 22)) {
-        // large inputs: exp from the table, persistent CTAs
-        const uint16_t* table = bf16_table<1>();
-        auto kern = softmax_bf16_kernel<false, true>;
-        if (table && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTabBytes) == cudaSuccess) {
-            const int64_t ctas = (rows + kTabThreads / 32 - 1) / (kTabThreads / 32);
-            kern<<<(unsigned)std::min<int64_t>(ctas, sm_count()), kTabThreads, kTabBytes, st>>>(xs, os, table, rows, (int)cols);
-            return check_launch();
-        }
+        // large inputs: the persistent kernel with the exp table and row prefetch (softmax_quantize_mx.cu)
+        const int rc = softmax_rows_large(x, out, rows, cols, st);
+        if (rc == MXQ_OK) return rc;
         cudaGetLastError();
     }
     const int64_t ctas = (rows + kSmThreads / 32 - 1) / (kSmThreads / 32);

@@ -34,5 +34,7 @@ __device__ __forceinline__ void silu_chain(float q, float& s, float& y) {
 // Device table of the sigmoid chain for every bfloat16 bit pattern (64 Ki entries of 2 bytes), built on
 // first use on the current device by running silu_chain on each pattern; nullptr on failure.
 const uint16_t* sigmoid_table();
+// The same for exp rounded to bfloat16 (the numerator of the softmax chain, mx/softmax.py:28-33).
+const uint16_t* exp_table();
 
 }  // namespace mxq

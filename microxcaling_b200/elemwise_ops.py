@@ -132,6 +132,12 @@ def quantize_elemwise_op(A, mx_specs, round=None):
             from . import _backend
             return _backend.quantize_elemwise(A.contiguous(), 9, 8, _get_max_norm(8, 9), 2, False, True,
                                               out_dtype=torch.bfloat16)
+        if not A.is_cuda and A.dtype == torch.float32 and mx_specs["custom_cuda"] and A.layout == torch.strided \
+                and A.is_pinned() and A.is_contiguous():
+            # pinned host tensor with custom_cuda: rounded on the GPU, chunked, result in pinned memory
+            from . import _backend
+            return _backend.quantize_elemwise_host(A, 9, 8, _get_max_norm(8, 9), 2, False, True,
+                                                   out_dtype=torch.bfloat16)
         return A.to(torch.bfloat16)
     if mx_specs["bfloat"] > 0 and mx_specs["fp"] > 0:
         raise ValueError("Cannot set both [bfloat] and [fp] in mx_specs.")

@@ -1,14 +1,17 @@
 """Process-wide injection of the MX operators into the torch namespaces
 (reference: mx/mx_mapping.py:26-122).  Every mapped function and module takes
 `mx_specs`; the injected wrappers supply it.  Only the operators this package
-implements are mapped: linear / matmul / mm / addmm / bmm, softmax, silu and
-the four arithmetic functions; the reference's convolution, normalisation,
+implements are mapped: linear / matmul / mm / addmm / bmm, the convolutions,
+softmax, silu and the four arithmetic functions; the reference's normalisation,
 pooling, recurrent and remaining activation layers keep their stock torch
 implementations."""
+from contextlib import contextmanager
+
 import torch
 
 from .activations import SiLU, silu
 from .bmm import bmm
+from .convolution import Conv1d, Conv2d, Conv3d, ConvTranspose2d, conv1d, conv2d, conv3d
 from .linear import Linear, linear
 from .matmul import MatMulFunction, matmul
 from .simd_ops import simd_add, simd_div, simd_mul, simd_sub
@@ -35,9 +38,11 @@ def addmm_mx(bias, in1, in2, mx_specs=None, name=None):
     return MatMulFunction.apply(in1, in2, bias, apply_mx_specs(mx_specs), name)
 
 
-MODULE_MAPPING = {"Linear": Linear, "SiLU": SiLU, "Softmax": Softmax}
+MODULE_MAPPING = {"Linear": Linear, "SiLU": SiLU, "Softmax": Softmax, "Conv1d": Conv1d, "Conv2d": Conv2d,
+                  "Conv3d": Conv3d, "ConvTranspose2d": ConvTranspose2d}
 FUNCTION_MAPPING = {
     "linear": linear, "matmul": matmul, "mm": matmul, "addmm": addmm_mx, "bmm": bmm,
+    "conv1d": conv1d, "conv2d": conv2d, "conv3d": conv3d,
     "softmax": softmax, "silu": silu,
     "add": simd_add, "sub": simd_sub, "mul": simd_mul, "div": simd_div,
 }
@@ -59,3 +64,28 @@ def inject_pyt_ops(mx_specs):
             torch.nn.functional.__dict__[k] = tracer_decorator(v, mx_specs)
     for k, v in MODULE_MAPPING.items():
         torch.nn.__dict__[k] = bind_module(v)
+
+
+# The stock callables, captured when this module is imported (before any injection).
+_STOCK = {"torch": {k: torch.__dict__[k] for k in FUNCTION_MAPPING if k in torch.__dict__},
+          "functional": {k: torch.nn.functional.__dict__[k] for k in FUNCTION_MAPPING
+                         if k in torch.nn.functional.__dict__},
+          "nn": {k: torch.nn.__dict__[k] for k in MODULE_MAPPING}}
+
+
+def restore_pyt_ops():
+    """Undo inject_pyt_ops: put the stock torch callables and modules back (the reference has no
+    counterpart; its injection lasts for the life of the process)."""
+    torch.__dict__.update(_STOCK["torch"])
+    torch.nn.functional.__dict__.update(_STOCK["functional"])
+    torch.nn.__dict__.update(_STOCK["nn"])
+
+
+@contextmanager
+def injected(mx_specs):
+    """`with injected(specs):` = inject_pyt_ops(specs) for the duration of the block."""
+    inject_pyt_ops(mx_specs)
+    try:
+        yield
+    finally:
+        restore_pyt_ops()

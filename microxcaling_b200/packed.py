@@ -150,3 +150,28 @@ class PackedMX:
         codes = buf[:nc].reshape(batch, rows, K).to(device)
         scales = buf[nc:].clone().to(device)
         return cls(codes, scales, container, ebits, mbits, scale_bits, batch, rows, K)
+
+
+# ---------------------------------------------------------------------------------------------
+# A tensor can carry the packed form of its own values: the fused softmax writes the probabilities
+# and their MX packing in one pass, and the product that consumes the probabilities picks the
+# packing up instead of quantizing them again.  The note is only honoured while the tensor is
+# unchanged (same storage pointer, same version counter) and for the same format and rounding.
+# ---------------------------------------------------------------------------------------------
+def _note_key(t, fmt, round, specs):
+    return (t.data_ptr(), t._version, tuple(t.shape), str(fmt), round, specs["scale_bits"] or 8,
+            bool(specs["mx_flush_fp32_subnorms"]))
+
+
+def attach_packed(t, packed, fmt, round, specs):
+    """Remember on tensor `t` that `packed` is MX(t) along its last axis with (fmt, round)."""
+    t._mx_packed = (_note_key(t, fmt, round, specs), packed)
+    return t
+
+
+def packed_note(t, fmt, round, specs):
+    """The PackedMX attached to `t` for (fmt, round), if `t` still holds the values it was made from."""
+    note = getattr(t, "_mx_packed", None)
+    if note is None or note[0] != _note_key(t, fmt, round, specs):
+        return None
+    return note[1]

@@ -34,3 +34,8 @@ def golden_sweep():
 @pytest.fixture(scope="session")
 def golden_layers():
     return load_golden("layers.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_layers2():
+    return load_golden("layers2.npz")

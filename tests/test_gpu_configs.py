@@ -1,0 +1,269 @@
+"""GPU parity at the stated sizes of the layer configurations: the public layer API on CUDA tensors against
+the oracle on a random sample of outputs.
+
+Every product is checked stage by stage: the operands the GPU fed into a GEMM are quantized again by the CPU
+oracle (fp32 containers of the same bf16 values, blocks of 32 along the contraction axis), multiplied in double
+precision, rounded to bfloat16 the way mx_specs asks, and compared with the sampled GPU outputs.
+
+Tolerance (fp32 accumulation order only): an output may differ from the rounded double product only where that
+product lies within 2^-22 * sum|a_k b_k| of a bfloat16 rounding boundary, and then by one bf16 ulp; at least
+97 % of the sampled outputs must be equal."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import microxcaling_b200 as mx
+from microxcaling_b200.specs import finalize_mx_specs
+
+pytestmark = pytest.mark.gpu
+BF16_MAX = 3.3895313892515355e38
+
+
+def _bf16_round(x, mode="nearest"):
+    return oracle.quantize_elemwise(np.asarray(x, np.float32), 9, 8, BF16_MAX, mode).astype(np.float64)
+
+
+def _q(x, fmt, axis, rnd="nearest"):
+    """Oracle MX quantization of a float32 numpy array (bf16-representable values), block 32 along `axis`."""
+    return oracle.quantize_mx(np.ascontiguousarray(x, np.float32), fmt, axis=axis, block=32, scale_bits=8, round=rnd)
+
+
+def _check_product(got, a_q, b_q, name, rnd="nearest", min_exact=0.97):
+    """got [R, C] (GPU outputs, any float dtype as numpy float64) vs a_q [R, K] @ b_q [C, K]^T."""
+    ref, refabs = oracle.gemm_nt(a_q[None], b_q[None], want_abs=True)
+    ref, refabs = ref[0], refabs[0]
+    want = _bf16_round(ref, rnd)
+    err = 2.0 ** -22 * refabs + 1e-30
+    # the result is acceptable if it is the rounding of some value within the accumulation error of ref
+    lo, hi = _bf16_round(ref - err, rnd), _bf16_round(ref + err, rnd)
+    ok = (got >= np.minimum(lo, hi)) & (got <= np.maximum(lo, hi))
+    assert ok.all(), (name, int((~ok).sum()), float(np.abs(got - want).max()))
+    exact = float((got == want).mean())
+    assert exact >= min_exact, (name, exact)
+    return exact
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _sample(n, k, rng):
+    return np.sort(rng.choice(n, k, replace=False))
+
+
+def test_config3_linear_forward_backward_full_size():
+    """mx.Linear 8192 tokens x 4096 -> 4096, forward fp8_e4m3, backward fp8_e5m2, block 32, bfloat16: y,
+    grad_input and grad_weight on sampled rows x columns (axes of the three products: mx/linear.py:62-181)."""
+    M, K, N = 8192, 4096, 4096
+    sp = finalize_mx_specs({"w_elem_format": "fp8_e4m3", "a_elem_format": "fp8_e4m3", "w_elem_format_bp": "fp8_e5m2",
+                            "a_elem_format_bp": "fp8_e5m2", "a_elem_format_bp_ex": "fp8_e5m2",
+                            "a_elem_format_bp_os": "fp8_e5m2", "block_size": 32, "scale_bits": 8, "bfloat": 16,
+                            "custom_cuda": True})
+    torch.manual_seed(0)
+    layer = mx.Linear(K, N, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda().requires_grad_()
+    go = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    y = layer(x)
+    y.backward(go)
+    torch.cuda.synchronize()
+    from microxcaling_b200 import _backend
+    assert _backend.device_status() == 0
+    rng = np.random.default_rng(0)
+    w = layer.weight.detach()
+    rows, cols = _sample(M, 16, rng), _sample(N, 256, rng)
+    ti = lambda a: torch.as_tensor(a, device="cuda")
+    # y[r, c] = MX(x)[r, :] . MX(w)[c, :], blocks along in_features
+    _check_product(_np(y[ti(rows)][:, ti(cols)]).astype(np.float64), _q(_np(x[ti(rows)]), "fp8_e4m3", 1),
+                   _q(_np(w[ti(cols)]), "fp8_e4m3", 1), "y")
+    # grad_input[r, k] = MX(go)[r, :] . MX(w)[:, k], blocks along out_features
+    kk = _sample(K, 256, rng)
+    _check_product(_np(x.grad[ti(rows)][:, ti(kk)]).astype(np.float64), _q(_np(go[ti(rows)]), "fp8_e5m2", 1),
+                   _q(_np(w[:, ti(kk)]), "fp8_e5m2", 0).T.copy(), "grad_input")
+    # grad_weight[n, k] = MX(go)[:, n] . MX(x)[:, k], blocks along the token axis
+    nn = _sample(N, 16, rng)
+    _check_product(_np(layer.weight.grad[ti(nn)][:, ti(kk)]).astype(np.float64),
+                   _q(_np(go[:, ti(nn)]), "fp8_e5m2", 0).T.copy(), _q(_np(x.detach()[:, ti(kk)]), "fp8_e5m2", 0).T.copy(),
+                   "grad_weight")
+
+
+def test_config4_attention_block_full_size():
+    """S = mx.bmm(Q, K^T), P = mx.softmax(S), O = mx.bmm(P, V) at 32 heads x 2048 x 128, fp6_e3m2, block 32
+    along the contraction dimension, bfloat16.  S and O against the oracle on sampled heads / rows (O given
+    the GPU's own P); P against the vector-op chain of mx/softmax.py:18-41 composed of torch ops on the GPU
+    (one row sum whose fp32 order is unspecified: rows may differ by <= 2 bf16 ulp, >= 95 % equal)."""
+    Hh, S, D = 32, 2048, 128
+    sp = finalize_mx_specs({"a_elem_format": "fp6_e3m2", "block_size": 32, "scale_bits": 8, "bfloat": 16,
+                            "custom_cuda": True})
+    g = torch.Generator().manual_seed(0)
+    q, k, v = [(torch.randn(Hh, S, D, generator=g) * 128 ** -0.25).to(torch.bfloat16).cuda() for _ in range(3)]
+    kt = k.transpose(-1, -2).contiguous()
+    with torch.no_grad():
+        s = mx.bmm(q, kt, mx_specs=sp)
+        p = mx.softmax(s, dim=-1, mx_specs=sp)
+        o = mx.bmm(p, v, mx_specs=sp)
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(4)
+    ti = lambda a: torch.as_tensor(a, device="cuda")
+    for h in (0, 13, 31):
+        rows, cols = _sample(S, 16, rng), _sample(S, 256, rng)
+        _check_product(_np(s[h][ti(rows)][:, ti(cols)]).astype(np.float64), _q(_np(q[h][ti(rows)]), "fp6_e3m2", 1),
+                       _q(_np(kt[h][:, ti(cols)]), "fp6_e3m2", 0).T.copy(), "S head %d" % h)
+        dd = _sample(D, 64, rng)
+        _check_product(_np(o[h][ti(rows)][:, ti(dd)]).astype(np.float64), _q(_np(p[h][ti(rows)]), "fp6_e3m2", 1),
+                       _q(_np(v[h][:, ti(dd)]), "fp6_e3m2", 0).T.copy(), "O head %d" % h)
+    # softmax: the composed chain (max, sub, exp, sum, div; each step rounded to bfloat16 = computed in fp32, stored bf16)
+    h = 7
+    x = s[h].float()
+    m = x.max(dim=-1, keepdim=True).values
+    d = (x - m).to(torch.bfloat16).float()
+    e = torch.exp(d).to(torch.bfloat16).float()
+    ssum = e.sum(dim=-1, keepdim=True).to(torch.bfloat16).float()
+    want = (e / ssum).to(torch.bfloat16)
+    got = p[h]
+    same_rows = (got == want).all(dim=-1).float().mean().item()
+    ulp = want.float().abs().clamp_min(1e-30) * 2.0 ** -7
+    assert bool(((got.float() - want.float()).abs() <= 2 * ulp).all())
+    assert same_rows >= 0.95, same_rows
+
+
+def _build_injected_ffn(hidden, inter, sp, dev, dtype=torch.bfloat16):
+    """Config 5 the way it is specified: inject_pyt_ops first, then stock torch modules and functions
+    (plus the explicit mx.RMSNorm, which has no torch counterpart to inject over)."""
+    import torch.nn.functional as F
+    from microxcaling_b200 import mx_mapping
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm = mx.RMSNorm(hidden, eps=1e-5, mx_specs=sp)
+            self.gate = torch.nn.Linear(hidden, inter, bias=False)
+            self.up = torch.nn.Linear(hidden, inter, bias=False)
+            self.down = torch.nn.Linear(inter, hidden, bias=False)
+
+        def forward(self, x):
+            h = self.norm(x)
+            return self.down(torch.mul(F.silu(self.gate(h)), self.up(h)))
+
+    with mx_mapping.injected(sp):
+        blk = Block()
+        assert isinstance(blk.gate, mx.Linear)
+        return blk.to(dev).to(dtype)
+
+
+def test_config5_ffn_via_inject_pyt_ops_full_size(monkeypatch):
+    """Llama-style FFN (hidden 8192, intermediate 28672, 16384 tokens, w fp4_e2m1, a fp8_e4m3, block 32,
+    bfloat16) built from stock torch.nn.Linear / F.silu / torch.mul after inject_pyt_ops: the three products
+    must reach mxq_gemm_mx, and each is checked against the oracle on sampled tokens x features, given the
+    GPU's own inputs of that stage; SiLU(gate) * up against the torch chain."""
+    import torch.nn.functional as F
+    from microxcaling_b200 import _backend, mx_mapping
+    H, I, T = 8192, 28672, 16384
+    sp = finalize_mx_specs({"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32,
+                            "scale_bits": 8, "bfloat": 16, "custom_cuda": True})
+    torch.manual_seed(0)
+    blk = _build_injected_ffn(H, I, sp, "cuda").eval()
+    gemms = []
+    real = _backend.gemm_mx
+    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (gemms.append((a[5], a[6], a[7])), real(*a, **k))[1])
+    seen = {}
+    hooks = [m.register_forward_hook(lambda mod, inp, out, n=n: seen.__setitem__(n, (inp[0], out)))
+             for n, m in (("gate", blk.gate), ("up", blk.up), ("down", blk.down), ("norm", blk.norm))]
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(4, 4096, H, generator=gen).to(torch.bfloat16).cuda()
+    with torch.no_grad(), mx_mapping.injected(sp):
+        y = blk(x)
+    torch.cuda.synchronize()
+    for h_ in hooks:
+        h_.remove()
+    assert _backend.device_status() == 0
+    assert gemms == [(T, I, H), (T, I, H), (T, H, I)], gemms          # (M, N, K) of the three tensor-core products
+    assert y.shape == (4, 4096, H) and y.dtype == torch.bfloat16
+    rng = np.random.default_rng(5)
+    ti = lambda a: torch.as_tensor(a, device="cuda")
+    rows = _sample(T, 8, rng)
+    hn = seen["gate"][0].reshape(T, H)
+    for name, lin in (("gate", blk.gate), ("up", blk.up)):
+        cols = _sample(I, 256, rng)
+        out = seen[name][1].reshape(T, I)
+        _check_product(_np(out[ti(rows)][:, ti(cols)]).astype(np.float64), _q(_np(hn[ti(rows)]), "fp8_e4m3", 1),
+                       _q(_np(lin.weight.detach()[ti(cols)]), "fp4_e2m1", 1), name)
+    act = seen["down"][0].reshape(T, I)
+    cols = _sample(H, 256, rng)
+    _check_product(_np(y.reshape(T, H)[ti(rows)][:, ti(cols)]).astype(np.float64), _q(_np(act[ti(rows)]), "fp8_e4m3", 1),
+                   _q(_np(blk.down.weight.detach()[ti(cols)]), "fp4_e2m1", 1), "down")
+    # SiLU(gate) * up: the chain of mx/activations.py:418-439 and mx/simd_ops.py:154-187 in torch ops
+    gt, ut = seen["gate"][1].reshape(T, I)[ti(rows)].float(), seen["up"][1].reshape(T, I)[ti(rows)].float()
+    bf = lambda t: t.to(torch.bfloat16).float()
+    sig = bf(1.0 / bf(bf(torch.exp(-gt)) + 1.0))
+    want = bf(bf(gt * sig) * ut)
+    assert torch.equal(act[ti(rows)].float(), want)
+    # RMSNorm rows against the composed chain of mx/layernorm.py:113-129
+    xr = x.reshape(T, H)[ti(rows)].float()
+    ms = bf(bf((bf(xr * xr)).sum(-1, keepdim=True)) / H)
+    rinv = bf(1.0 / bf(torch.sqrt(bf(ms + 1e-5))))
+    wantn = bf(bf(blk.norm.weight.float() * bf(xr * rinv)) + blk.norm.bias.float())
+    gotn = seen["norm"][1].reshape(T, H)[ti(rows)].float()
+    assert bool(((gotn - wantn).abs() <= wantn.abs() * 2.0 ** -6 + 1e-30).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ffn_via_inject_pyt_ops_matches_reference_fixture(golden_layers2, monkeypatch, dtype):
+    """The same block at a reduced width against outputs recorded from the reference itself (built there
+    after the reference's inject_pyt_ops, CPU, fp32 containers): stage by stage on the recorded inputs of
+    each stage, and end to end.
+
+    fp32 CUDA tensors follow the fixture's arithmetic (fp32 containers, every vector step rounded half away
+    from zero by the rounding kernel): products within one bf16 ulp and >= 97 % equal, SiLU(gate) * up equal
+    but for the exp of another math library.  bfloat16 CUDA tensors are what the reference itself computes
+    differently: there every torch op rounds its fp32 result to nearest-EVEN bfloat16 storage and the
+    bfloat16 rounding step that follows finds nothing left to round, so exact ties land on the other
+    neighbour: the 16-bit products g * sigmoid and (.) * up tie about once in 256, and exp(-g) + 1 ties for
+    every exp(-g) in [256, 512); one such step moves the result by an ulp and the later steps add theirs:
+    <= 8 ulp, >= 75 % equal (exp(-g) in [0.5, 1) plus one needs nine bits, a tie every other time; the fused
+    kernels' own bit-exactness against the torch-composed bfloat16 chain is tested with the vector kernels)."""
+    import torch.nn.functional as F
+    from microxcaling_b200 import _backend, mx_mapping
+    meta, z = golden_layers2
+    m = [r for r in meta if r["op"] == "ffn"][0]
+    sp = finalize_mx_specs(dict(m["specs"], custom_cuda=True))
+    H, I = m["hidden"], m["inter"]
+    blk = _build_injected_ffn(H, I, sp, "cuda", dtype).eval()
+    t = lambda k: torch.tensor(z["ffn_" + k]).to(dtype).cuda()
+    with torch.no_grad():
+        blk.norm.weight.copy_(t("norm_w")); blk.norm.bias.copy_(t("norm_b"))
+        blk.gate.weight.copy_(t("wg")); blk.up.weight.copy_(t("wu")); blk.down.weight.copy_(t("wd"))
+    calls = []
+    real = _backend.gemm_mx
+    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    bf = dtype == torch.bfloat16
+
+    def close(got, name, key, max_ulp=1, min_exact=0.97):
+        a, b = got.float().cpu().numpy().astype(np.float64), z["ffn_" + key].astype(np.float64)
+        ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(b), 1e-30))) - 7)          # spacing of bf16 at b
+        assert (np.abs(a - b) <= max_ulp * ulp).all(), (name, float((np.abs(a - b) / ulp).max()))
+        assert float((a == b).mean()) >= min_exact, (name, float((a == b).mean()))
+
+    with torch.no_grad(), mx_mapping.injected(sp):
+        # RMSNorm: one fp32 row sum in unspecified order; a row whose rounded mean lands on the neighbouring
+        # bfloat16 value moves weight * x_norm of all its elements by an ulp or two, and the bias add that
+        # follows can cancel: the tolerance is in ulps of max(|weight * x_norm|, |result|)
+        hn = blk.norm(t("x")).float().cpu().numpy().astype(np.float64)
+        hr = z["ffn_h"].astype(np.float64)
+        scale = np.maximum(np.abs(hr), np.abs(hr - z["ffn_norm_b"].astype(np.float64)[None, :]))
+        assert (np.abs(hn - hr) <= 3 * 2.0 ** -7 * scale + 1e-30).all(), float(np.abs(hn - hr).max())
+        assert float((hn == hr).mean()) >= (0.85 if bf else 0.9)
+        close(blk.gate(t("h")), "gate", "gate")
+        close(blk.up(t("h")), "up", "up")
+        close(torch.mul(F.silu(t("gate")), t("up")), "act", "act", max_ulp=8 if bf else 1, min_exact=0.75 if bf else 0.999)
+        close(blk.down(t("act")), "down", "y")
+        n0 = len(calls)
+        # end to end the stages' one-ulp differences travel on: every output is a sum over the intermediate
+        # features, so the bound is relative to the size of the outputs of its token, not to the output itself
+        yb = blk(t("x")).float().cpu().numpy().astype(np.float64)
+        yr = z["ffn_y"].astype(np.float64)
+        row = np.sqrt((yr ** 2).mean(axis=1, keepdims=True))
+        assert (np.abs(yb - yr) <= 2.0 ** -5 * (np.abs(yr) + row)).all(), float((np.abs(yb - yr) / (np.abs(yr) + row)).max())
+        assert float((yb == yr).mean()) >= (0.4 if bf else 0.6)
+        assert len(calls) - n0 == 3

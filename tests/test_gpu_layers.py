@@ -25,7 +25,8 @@ def close_bf16(got, ref, name, min_exact=0.97):
     assert a.shape == b.shape, name
     ulp = np.maximum(np.abs(b), 1e-30) * 2.0 ** -7
     ok = np.abs(a - b) <= ulp
-    assert ok.all(), (name, np.abs(a - b).max(), int((~ok).sum()))
+    worst = np.unravel_index(np.argmax(np.abs(a - b) / ulp), a.shape)
+    assert ok.all(), (name, np.abs(a - b).max(), int((~ok).sum()), "worst at", worst, float(a[worst]), float(b[worst]))
     exact = float((a == b).mean())
     assert exact >= min_exact, (name, exact)
 
@@ -196,3 +197,59 @@ def test_linear_with_odd_feature_count_takes_the_tensor_core_path(monkeypatch):
     with torch.no_grad():
         want = lin(x)
     close_bf16(got, want.float().cpu().numpy(), "linear K=96")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layer_variants_match_reference(golden_layers2, dtype):
+    """mode_config aw / wa, matmul bias, addmm, quantize_backprop=False and per-tensor rounding modes on CUDA
+    tensors against outputs recorded from the reference.  With quantize_backprop=False the backward products
+    are plain (unquantized) torch GEMMs: compared in fp32 with a relative tolerance, only for fp32 tensors."""
+    from test_host_layers import _run_layers2_case
+    meta, z = golden_layers2
+    for m in meta:
+        if m["op"] == "ffn":
+            continue
+        nobp = m["specs"].get("quantize_backprop") is False
+        for name, (got, want) in _run_layers2_case(m, z, "cuda", dtype).items():
+            tag = m["tag"] + "." + name
+            if nobp and name != "y":
+                if dtype == torch.float32:
+                    a = got.detach().float().cpu().numpy()
+                    assert np.allclose(a, want, rtol=1e-4, atol=1e-4 * np.abs(want).max()), tag
+                continue
+            if m["tag"] == "mm_bias_3d_shared" and name == "gb" and dtype == torch.bfloat16:
+                # gradient of a right operand shared by the batch: autograd sums the per-batch products in the
+                # tensor's dtype, so bfloat16 storage rounds that sum once more than the fp32 containers do
+                # (and a per-batch product that lands on the neighbouring bfloat16 value moves the sum by an ulp
+                # of that product, not of the sum)
+                a = got.detach().float().cpu().numpy().astype(np.float64)
+                assert (np.abs(a - want) <= np.abs(want) * 2.0 ** -7 + np.abs(want).max() * 2.0 ** -6).all(), tag
+                continue
+            bias_grad = name in ("gbias", "gb") and got.dim() == 1
+            if bias_grad and dtype == torch.bfloat16 and m["specs"].get("round_grad_weight") == "floor":
+                # the bias gradient is a torch sum: on bfloat16 storage torch rounds it to nearest-even before the
+                # 'floor' rounding step sees it (nothing left to round), on fp32 containers the fp32 sum is
+                # rounded toward zero: half of the values sit one ulp apart
+                close_bf16(got, want, tag, min_exact=0.3)
+                continue
+            close_bf16(got, want, tag, min_exact=0.9 if bias_grad else 0.97)
+
+
+def test_mx_quantization_over_two_axes_on_cuda(golden_sweep):
+    """Several shared axes on a CUDA tensor (the reference handles them with torch ops on the tensor's
+    device, mx/mx_ops.py:228-296): equals the host formulation; and shared_exp_method='none'."""
+    from microxcaling_b200.mx_ops import _quantize_mx
+    torch.manual_seed(3)
+    x = torch.randn(6, 40, 24) * 3
+    for axes, bs in (([0, 2], 4), ([-1, -2], 8), ([1, 2], 32)):
+        for fmt in ("fp8_e4m3", "int8", "fp4_e2m1"):
+            for rnd in ("nearest", "even"):
+                want = _quantize_mx(x, 8, fmt, axes=axes, block_size=bs, round=rnd)
+                got = _quantize_mx(x.cuda(), 8, fmt, axes=axes, block_size=bs, round=rnd)
+                assert got.is_cuda and torch.equal(got.cpu(), want), (axes, bs, fmt, rnd)
+    want = _quantize_mx(x, 8, "fp6_e2m3", shared_exp_method="none", axes=[-1], block_size=32)
+    got = _quantize_mx(x.cuda(), 8, "fp6_e2m3", shared_exp_method="none", axes=[-1], block_size=32)
+    assert torch.equal(got.cpu(), want)
+    xb = x.to(torch.bfloat16)
+    got = _quantize_mx(xb.cuda(), 8, "fp8_e4m3", axes=[0, 1], block_size=2)
+    assert got.dtype == torch.bfloat16 and torch.equal(got.cpu(), _quantize_mx(xb, 8, "fp8_e4m3", axes=[0, 1], block_size=2))

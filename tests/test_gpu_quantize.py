@@ -305,3 +305,36 @@ def test_host_buffer_pipeline(be, shape, axis):
     e_want = be.quantize_elemwise(xf.cuda(), 5, 8, 2.0 ** 127 * 1.875, 2).cpu()
     e_got = be.quantize_elemwise_host(xf, 5, 8, 2.0 ** 127 * 1.875, 2)
     assert torch.equal(e_got, e_want)
+
+
+def test_dither_with_caller_noise(be):
+    """round='dither' = floor(|x| / quantum + noise) (mx/elemwise_ops.py:57-59, PyTorch-only in the
+    reference, which draws the noise itself).  With the noise tensor supplied by the caller the GPU kernels
+    (MX along both axes, fp32 / bf16 storage, and the elementwise kernel) must equal the torch formulation
+    for CPU tensors and the library's host quantizer, value for value."""
+    from microxcaling_b200.mx_ops import _quantize_mx
+    from microxcaling_b200.elemwise_ops import _quantize_elemwise_core
+    torch.manual_seed(11)
+    x = torch.randn(96, 160) * torch.exp2(torch.randint(-6, 6, (96, 160)).float())
+    n = torch.rand(96, 160)
+    for dt in (torch.float32, torch.bfloat16):
+        xd = x.to(dt)
+        for fmt in ("fp8_e4m3", "fp6_e2m3", "fp4_e2m1", "int8"):
+            for axis in (0, 1):
+                want = _quantize_mx(xd, 8, fmt, axes=[axis], block_size=32, round="dither", noise=n)
+                twin = _quantize_mx(xd, 8, fmt, axes=[axis], block_size=32, round="dither", noise=n, custom_cuda=True)
+                got = _quantize_mx(xd.cuda(), 8, fmt, axes=[axis], block_size=32, round="dither", noise=n.cuda())
+                assert oracle.same_values(to_np(got), to_np(want)), (dt, fmt, axis)
+                assert oracle.same_values(to_np(twin), to_np(want)), (dt, fmt, axis, "host quantizer")
+                # dither never moves a value by more than one quantum from its floor
+                lo = _quantize_mx(xd, 8, fmt, axes=[axis], block_size=32, round="floor")
+                assert bool((want.float().abs() >= lo.float().abs()).all())
+        for bits, eb, mn in ((5, 8, 2.0 ** 127 * 1.75), (7, 5, 57344.0), (8, 0, 1.984375)):
+            want = _quantize_elemwise_core(xd, bits, eb, mn, "dither", noise=n)
+            got = _quantize_elemwise_core(xd.cuda(), bits, eb, mn, "dither", noise=n.cuda())
+            assert oracle.same_values(to_np(got), to_np(want)), (dt, bits, eb)
+    # two different noise tensors give different results; the same one is reproducible
+    a = _quantize_mx(x.cuda(), 8, "fp4_e2m1", axes=[1], block_size=32, round="dither", noise=n.cuda())
+    b = _quantize_mx(x.cuda(), 8, "fp4_e2m1", axes=[1], block_size=32, round="dither", noise=torch.rand(96, 160).cuda())
+    assert not torch.equal(a, b)
+    assert torch.equal(a, _quantize_mx(x.cuda(), 8, "fp4_e2m1", axes=[1], block_size=32, round="dither", noise=n.cuda()))

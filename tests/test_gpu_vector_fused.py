@@ -224,3 +224,71 @@ def test_swiglu_quantize_equals_two_steps(fmt, rnd, gemm_layout):
     c_got, s_got = be.swiglu_quantize_mx(gate2, up2, 8, eb, mb, mn, False, rnd, gemm_layout=gemm_layout)
     assert torch.equal(c_got, c_want)
     assert torch.equal(s_got.view(-1), s_want.view(-1))
+
+
+@pytest.mark.parametrize("fmt", ["fp6_e3m2", "fp8_e4m3", "fp8_e5m2", "fp4_e2m1"])
+@pytest.mark.parametrize("rnd", [0, 1, 2])
+def test_softmax_quantize_equals_two_steps(fmt, rnd):
+    """mxq_softmax_quantize_mx = mxq_softmax_bf16 followed by mxq_quantize_mx (codes + scales in the GEMM
+    layout): probabilities, code bytes and scale bytes all equal, for rows with ordinary logits, with a
+    dominant logit (probabilities spanning the whole bfloat16 range, zeros included), -inf entries and a
+    NaN row; with and without the probabilities being written."""
+    import oracle
+    from microxcaling_b200 import _backend as be
+    eb, mb, mn = oracle.FORMATS[fmt]
+    torch.manual_seed(1)
+    x = torch.randn(3, 160, 2048, device="cuda") * 1.5
+    x[0, 1, ::7] += 40.0
+    x[0, 2, 5] = 90.0
+    x[1, 3, 100:400] = float("-inf")
+    x[2, 4, 17] = float("nan")
+    x[2, 5, :] = -1e30
+    x = x.to(torch.bfloat16)
+    for cols in (2048, 96):
+        xs = x[..., :cols].contiguous()
+        p, codes, scales = be.softmax_quantize_mx(xs, 8, eb, mb, mn, False, rnd, rows_per_batch=xs.shape[-2])
+        p2 = be.softmax_bf16(xs)
+        _, c2, s2 = be.quantize_mx(p2.reshape(-1, cols), 8, eb, mb, mn, 32, 1, False, rnd, want_dq=False,
+                                   want_codes=True, gemm_layout=True, rows_per_batch=xs.shape[-2])
+        assert same(p, p2), (fmt, rnd, cols)
+        assert torch.equal(codes.reshape(-1, cols), c2), (fmt, rnd, cols)
+        assert torch.equal(scales, s2), (fmt, rnd, cols)
+        none, c3, s3 = be.softmax_quantize_mx(xs, 8, eb, mb, mn, False, rnd, rows_per_batch=xs.shape[-2], want_probs=False)
+        assert none is None and torch.equal(c3, codes) and torch.equal(s3, scales)
+
+
+def test_softmax_hands_its_packing_to_the_next_product(monkeypatch):
+    """mx.softmax on batched score matrices writes the MX packing of the probabilities in the same pass and
+    mx.bmm picks it up: only the right operand is quantized by the product, the result equals the unfused
+    sequence, and a changed probability tensor is packed again."""
+    from microxcaling_b200 import _backend
+    sp = finalize_mx_specs({"a_elem_format": "fp6_e3m2", "block_size": 32, "scale_bits": 8, "bfloat": 16,
+                            "custom_cuda": True})
+    torch.manual_seed(0)
+    s = (torch.randn(8, 512, 1024, device="cuda") * 2).to(torch.bfloat16)
+    v = torch.randn(8, 1024, 64, device="cuda").to(torch.bfloat16)
+    packs = []
+    real = _backend.quantize_mx
+    monkeypatch.setattr(_backend, "quantize_mx", lambda A, *a, **k: (packs.append(tuple(A.shape)), real(A, *a, **k))[1])
+    with torch.no_grad():
+        p = mx.softmax(s, dim=-1, mx_specs=sp)
+        assert getattr(p, "_mx_packed", None) is not None
+        n0 = len(packs)
+        o = mx.bmm(p, v, mx_specs=sp)
+        assert len(packs) - n0 == 1                              # V only
+        p_plain = _backend.softmax_bf16(s)
+        assert same(p, p_plain)
+        n0 = len(packs)
+        o_plain = mx.bmm(p_plain, v, mx_specs=sp)
+        assert len(packs) - n0 == 2
+        assert torch.equal(o, o_plain)
+        p.mul_(0.5)                                              # the note no longer describes the tensor
+        n0 = len(packs)
+        o_half = mx.bmm(p, v, mx_specs=sp)
+        assert len(packs) - n0 == 2
+        assert torch.equal(o_half, mx.bmm(p_plain * 0.5, v, mx_specs=sp))
+    # with autograd the backward pass still sees the probabilities
+    s2 = s.clone().requires_grad_()
+    p2 = mx.softmax(s2, dim=-1, mx_specs=sp)
+    mx.bmm(p2, v, mx_specs=sp).sum().backward()
+    assert s2.grad is not None and torch.isfinite(s2.grad.float()).all()

@@ -147,3 +147,86 @@ def test_gradcheck_no_quantization():
     c = torch.randn(2, 4, 5, dtype=torch.float64, requires_grad=True)
     assert torch.autograd.gradcheck(lambda u, v: mx.bmm(u, v, mx_specs=sp), (a, c))
     assert torch.autograd.gradcheck(lambda u, v: mx.matmul(u, v, mx_specs=sp), (a, c))
+
+
+def _run_layers2_case(m, z, dev, dtype):
+    """Runs one recorded case of layers2.npz; returns {name: (got tensor, recorded array)}."""
+    from microxcaling_b200 import mx_mapping
+    sp = finalize_mx_specs(dict(m["specs"], custom_cuda=(dev != "cpu")))
+    t = m["tag"]
+    ld = lambda k, grad=True: torch.tensor(z[t + "_" + k]).to(dev, dtype).requires_grad_(grad)
+    go = ld("go", False)
+    out = {}
+    if m["op"] in ("matmul", "addmm"):
+        a, b = ld("a"), ld("b")
+        bias = ld("bias") if m["bias"] else None
+        if m["op"] == "addmm":
+            y = mx_mapping.addmm_mx(bias, a, b, mx_specs=sp)
+        else:
+            y = mx.matmul(a, b, bias=bias, mx_specs=sp, mode_config=m["mode_config"])
+        y.backward(go)
+        out = {"y": (y, z[t + "_y"]), "ga": (a.grad, z[t + "_ga"]), "gb": (b.grad, z[t + "_gb"])}
+        if bias is not None:
+            out["gbias"] = (bias.grad, z[t + "_gbias"])
+    elif m["op"] == "bmm":
+        a, b = ld("a"), ld("b")
+        y = mx.bmm(a, b, mx_specs=sp)
+        y.backward(go)
+        out = {"y": (y, z[t + "_y"]), "ga": (a.grad, z[t + "_ga"]), "gb": (b.grad, z[t + "_gb"])}
+    elif m["op"] in ("conv1d", "conv2d", "conv3d", "convT2d"):
+        x, w = ld("x"), ld("w")
+        b = ld("b") if m["bias"] else None
+        fn = {"conv1d": mx.conv1d, "conv2d": mx.conv2d, "conv3d": mx.conv3d, "convT2d": mx.conv_transpose2d}[m["op"]]
+        y = fn(x, w, b, mx_specs=sp, **m["geom"])
+        y.backward(go)
+        out = {"y": (y, z[t + "_y"]), "gx": (x.grad, z[t + "_gx"]), "gw": (w.grad, z[t + "_gw"])}
+        if b is not None:
+            out["gb"] = (b.grad, z[t + "_gb"])
+    elif m["op"] == "linear":
+        x, w = ld("x"), ld("w")
+        b = ld("b") if m["bias"] else None
+        y = mx.linear(x, w, b, mx_specs=sp)
+        y.backward(go)
+        out = {"y": (y, z[t + "_y"]), "gx": (x.grad, z[t + "_gx"]), "gw": (w.grad, z[t + "_gw"])}
+        if b is not None:
+            out["gb"] = (b.grad, z[t + "_gb"])
+    return out
+
+
+def test_layer_variants_match_reference(golden_layers2):
+    """mode_config aw / wa, matmul bias, addmm, quantize_backprop=False, per-tensor rounding modes and the
+    convolutions: on CPU tensors the layers follow the reference's construction, so values must match exactly."""
+    meta, z = golden_layers2
+    assert {m["tag"] for m in meta} >= {"mm_aw", "mm_wa", "mm_bias", "addmm", "lin_nobp", "bmm_nobp", "lin_rounds",
+                                        "mm_rounds", "conv2d", "conv1d_groups", "conv3d", "convT2d"}
+    for m in meta:
+        if m["op"] == "ffn":
+            continue
+        for name, (got, want) in _run_layers2_case(m, z, "cpu", torch.float32).items():
+            assert _same(got, want), (m["tag"], name)
+
+
+def test_ffn_via_inject_pyt_ops_matches_reference_on_cpu(golden_layers2):
+    """The gated feed-forward block built from stock torch modules after inject_pyt_ops equals the
+    block the reference builds the same way (CPU tensors: exact)."""
+    import torch.nn.functional as F
+    from microxcaling_b200 import mx_mapping
+    meta, z = golden_layers2
+    m = [r for r in meta if r["op"] == "ffn"][0]
+    sp = finalize_mx_specs(dict(m["specs"], custom_cuda=False))
+    H, I = m["hidden"], m["inter"]
+    t = lambda k: torch.tensor(z["ffn_" + k])
+    norm = mx.RMSNorm(H, eps=1e-5, mx_specs=sp)
+    with mx_mapping.injected(sp):
+        gate, up, down = torch.nn.Linear(H, I, bias=False), torch.nn.Linear(H, I, bias=False), torch.nn.Linear(I, H, bias=False)
+        assert isinstance(gate, mx.Linear)
+        with torch.no_grad():
+            norm.weight.copy_(t("norm_w")); norm.bias.copy_(t("norm_b"))
+            gate.weight.copy_(t("wg")); up.weight.copy_(t("wu")); down.weight.copy_(t("wd"))
+            h = norm(t("x"))
+            g_, u_ = gate(h), up(h)
+            act = torch.mul(F.silu(g_), u_)
+            y = down(act)
+    assert torch.nn.Linear is not type(gate) and not issubclass(torch.nn.Linear, mx.Linear)   # restored
+    for name, got in (("h", h), ("gate", g_), ("up", u_), ("act", act), ("y", y)):
+        assert _same(got, z["ffn_" + name]), name

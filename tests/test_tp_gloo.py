@@ -46,6 +46,12 @@ def _worker(rank, world, port, q):
         # row-sharded quantization needs no exchange: each rank's rows are independent along the last axis
         qs = quantize_mx_op(x[lo:hi], sp, elem_format="fp8_e4m3", axes=[-1])
         q.put((rank, y, qs))
+        # the ranks disagree on whether the scattering GEMM may be used (one rank's environment forbids
+        # it): the choice is made collectively, so every rank must end up on the same branch
+        from microxcaling_b200 import tp as tpmod
+        tpmod._local_scatter_eligible = lambda device, world_: rank == 0
+        ffn._scatter = None
+        q.put((rank, "scatter=%s" % ffn._use_scatter(torch.device("cpu")), None))
         # mismatched shard sizes must be refused before any collective is entered
         try:
             ffn(x[lo:hi - 1])
@@ -75,13 +81,13 @@ def test_tp_ffn_two_ranks_matches_single_process():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    got = [q.get(timeout=240) for _ in range(4)]
+    got = [q.get(timeout=240) for _ in range(6)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
     outs = {r: (y, qs) for r, y, qs in got if isinstance(y, torch.Tensor)}
     flags = sorted(v for _, v, _ in got if isinstance(v, str))
-    assert flags == ["refused", "refused"]
+    assert flags == ["refused", "refused", "scatter=False", "scatter=False"]
     y = torch.cat([outs[0][0], outs[1][0]])
     qs = torch.cat([outs[0][1], outs[1][1]])
     assert torch.equal(qs, q_ref)                       # sharded quantization == whole-tensor quantization

@@ -83,3 +83,35 @@ def test_static_scratch_rejects_oversize_and_bad_shapes():
     assert L.mxq_linear_fwd_static(*args(1 << 30, 1 << 20)) == -5
     assert L.mxq_linear_fwd_static(*args(128, 100)) == -2                # K not a multiple of 128
     torch.cuda.synchronize()
+
+
+def test_static_entry_point_allocates_nothing_and_runs_at_its_limit():
+    """What the entry point is for: device memory in use does not move across a call once the first call
+    on the device has looked the array up.  The call is made at exactly the documented limit
+    (ceil(M/128)*128 * K == 32 Mi), where the scratch layout ends at the end of the fixed array, and its
+    result is compared with the workspace entry point."""
+    L = _lib()
+    M, K, N = 8192, 4096, 128
+    assert M * K == L.mxq_linear_static_max_elems()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    wc, ws = _pack_weight(L, w, st)
+    common = [x.data_ptr(), 2, M, K, E4M3[0], E4M3[1], E4M3[2], 0, 8, 0, wc.data_ptr(), ws.data_ptr(), N, 0]
+    tail = [2, 16, 0, None]
+    y_ws = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    y_st = torch.ones(M, N, dtype=torch.bfloat16, device="cuda")
+    need = L.mxq_linear_workspace_bytes(M, K)
+    wsp = torch.empty(need, dtype=torch.uint8, device="cuda")
+    assert L.mxq_linear_fwd(*common, y_ws.data_ptr(), *tail, wsp.data_ptr(), need, st) == 0
+    assert L.mxq_linear_fwd_static(*common, y_st.data_ptr(), *tail, st) == 0       # warm-up (first-call set-up)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    y_st.fill_(1.0)
+    assert L.mxq_linear_fwd_static(*common, y_st.data_ptr(), *tail, st) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)              # no cudaMalloc, no torch allocation behind the call
+    assert L.mxq_linear_static_status() == 0
+    assert torch.equal(y_st.view(torch.int16), y_ws.view(torch.int16))
