@@ -8,8 +8,9 @@ from .quantize import quantize_bfloat  # noqa: F401
 from .linear import Linear, linear  # noqa: F401
 from .matmul import matmul  # noqa: F401
 from .bmm import bmm  # noqa: F401
-from .activations import SiLU, silu  # noqa: F401
+from .activations import SiLU, silu, sigmoid, tanh  # noqa: F401
 from .layernorm import RMSNorm  # noqa: F401
 from .simd_ops import simd_add, simd_sub, simd_mul, simd_div  # noqa: F401
 from .softmax import Softmax, softmax  # noqa: F401
 from .convolution import Conv1d, Conv2d, Conv3d, ConvTranspose2d, conv1d, conv2d, conv3d, conv_transpose2d  # noqa: F401
+from .rnn import LSTM  # noqa: F401

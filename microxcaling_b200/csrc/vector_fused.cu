@@ -262,22 +262,15 @@ constexpr int kSmMaxVec = 8;
 
 __device__ __forceinline__ float nan_max(float a, float b) { return (b > a || b != b) ? b : a; }   // NaN wins, like torch.max
 
-// TAB: exp(d) of the bfloat16 value d comes from the 64 Ki-entry table (shared memory, persistent
-// 1024-thread CTAs).  The division e / s is done as e * (1/s) with 1/s correctly rounded: e and s have 8
-// significant bits each, so e / s is never a bfloat16 rounding midpoint and stays at least 2^-17 (relative)
-// away from one, far more than the 2^-23 error of the product, hence the bfloat16 result is the one of the
-// exact division; quotients that would round in bfloat16's subnormal range take the exact division.
-template <bool EXP2, bool TAB>
-__global__ void __launch_bounds__(TAB ? kTabThreads : kSmThreads)
-softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const uint16_t* __restrict__ table,
-                    const int64_t rows, const int cols) {
-    extern __shared__ uint4 exp_tab_smem[];
-    constexpr int kThreads = TAB ? kTabThreads : kSmThreads;
-    if (TAB) {
-        for (int i = threadIdx.x; i < kTabBytes / 16; i += kThreads) exp_tab_smem[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
-        __syncthreads();
-    }
-    const uint16_t* tab = reinterpret_cast<const uint16_t*>(exp_tab_smem);
+// Small inputs and exp2; large inputs run the persistent kernel of softmax_quantize_mx.cu (exp from a table,
+// rows prefetched into shared memory).  The division e / s is done as e * (1/s) with 1/s correctly rounded: e
+// and s have 8 significant bits each, so e / s is never a bfloat16 rounding midpoint and stays at least 2^-17
+// (relative) away from one, far more than the 2^-23 error of the product, hence the bfloat16 result is the one
+// of the exact division; quotients that would round in bfloat16's subnormal range take the exact division.
+template <bool EXP2>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, const int64_t rows, const int cols) {
+    constexpr int kThreads = kSmThreads;
     const int lane = threadIdx.x & 31;
     const int nchunk = cols >> 3;
     const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
@@ -304,13 +297,8 @@ softmax_bf16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t d2 = rb2(bf_lo(w[k][i]) - m, bf_hi(w[k][i]) - m);
-                    uint32_t e2;
-                    if (TAB) {
-                        e2 = (uint32_t)tab[d2 & 0xffffu] | ((uint32_t)tab[d2 >> 16] << 16);
-                    } else {
-                        const float d0 = bf_lo(d2), d1 = bf_hi(d2);
-                        e2 = rb2(EXP2 ? exp2f(d0) : expf(d0), EXP2 ? exp2f(d1) : expf(d1));
-                    }
+                    const float d0 = bf_lo(d2), d1 = bf_hi(d2);
+                    const uint32_t e2 = rb2(EXP2 ? exp2f(d0) : expf(d0), EXP2 ? exp2f(d1) : expf(d1));
                     acc += bf_lo(e2);
                     acc += bf_hi(e2);
                     w[k][i] = e2;
@@ -405,7 +393,7 @@ extern "C" int mxq_softmax_bf16(const void* x, void* out, int64_t rows, int64_t 
     }
     const int64_t ctas = (rows + kSmThreads / 32 - 1) / (kSmThreads / 32);
     const unsigned grid = (unsigned)std::min<int64_t>(ctas, (int64_t)sm_count() * 8);
-    if (use_exp2) softmax_bf16_kernel<true, false><<<grid, kSmThreads, 0, st>>>(xs, os, nullptr, rows, (int)cols);
-    else softmax_bf16_kernel<false, false><<<grid, kSmThreads, 0, st>>>(xs, os, nullptr, rows, (int)cols);
+    if (use_exp2) softmax_bf16_kernel<true><<<grid, kSmThreads, 0, st>>>(xs, os, rows, (int)cols);
+    else softmax_bf16_kernel<false><<<grid, kSmThreads, 0, st>>>(xs, os, rows, (int)cols);
     return check_launch();
 }

@@ -2,18 +2,19 @@
 (reference: mx/mx_mapping.py:26-122).  Every mapped function and module takes
 `mx_specs`; the injected wrappers supply it.  Only the operators this package
 implements are mapped: linear / matmul / mm / addmm / bmm, the convolutions,
-softmax, silu and the four arithmetic functions; the reference's normalisation,
-pooling, recurrent and remaining activation layers keep their stock torch
-implementations."""
+the LSTM, softmax, silu, sigmoid, tanh and the four arithmetic functions; the
+reference's normalisation, pooling and remaining activation layers keep their
+stock torch implementations."""
 from contextlib import contextmanager
 
 import torch
 
-from .activations import SiLU, silu
+from .activations import SiLU, sigmoid, silu, tanh
 from .bmm import bmm
 from .convolution import Conv1d, Conv2d, Conv3d, ConvTranspose2d, conv1d, conv2d, conv3d
 from .linear import Linear, linear
 from .matmul import MatMulFunction, matmul
+from .rnn import LSTM
 from .simd_ops import simd_add, simd_div, simd_mul, simd_sub
 from .softmax import Softmax, softmax
 from .specs import apply_mx_specs
@@ -39,11 +40,11 @@ def addmm_mx(bias, in1, in2, mx_specs=None, name=None):
 
 
 MODULE_MAPPING = {"Linear": Linear, "SiLU": SiLU, "Softmax": Softmax, "Conv1d": Conv1d, "Conv2d": Conv2d,
-                  "Conv3d": Conv3d, "ConvTranspose2d": ConvTranspose2d}
+                  "Conv3d": Conv3d, "ConvTranspose2d": ConvTranspose2d, "LSTM": LSTM}
 FUNCTION_MAPPING = {
     "linear": linear, "matmul": matmul, "mm": matmul, "addmm": addmm_mx, "bmm": bmm,
     "conv1d": conv1d, "conv2d": conv2d, "conv3d": conv3d,
-    "softmax": softmax, "silu": silu,
+    "softmax": softmax, "silu": silu, "sigmoid": sigmoid, "tanh": tanh,
     "add": simd_add, "sub": simd_sub, "mul": simd_mul, "div": simd_div,
 }
 

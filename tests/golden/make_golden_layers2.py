@@ -134,6 +134,25 @@ def main():
              (16, 32, 2, 2, 2), True)
     run_conv("convT2d", s_fp8, "convT2d", (32, 32, 5, 5), (32, 24, 3, 3), True, stride=2, padding=1)
 
+    # ---- LSTM: two layers, both directions (mx.linear products + bfloat-emulated gate arithmetic) ----
+    specs = dict(s_fp8)
+    sp = finalize_mx_specs(dict(specs, custom_cuda=False))
+    torch.manual_seed(77)
+    lstm = mx.LSTM(32, 64, num_layers=2, bidirectional=True, mx_specs=sp)
+    with torch.no_grad():
+        for prm in lstm.parameters():
+            prm.copy_(bf(prm))
+    x = bf(torch.randn(5, 32, 32, generator=g)).requires_grad_()
+    out, (hn, cn) = lstm(x)
+    go = bf(torch.randn(*out.shape, generator=g))
+    out.backward(go)
+    rec("lstm", x=x, go=go, out=out, hn=hn, cn=cn, gx=x.grad)
+    for k, v in lstm.state_dict().items():
+        rec("lstm", **{"p_" + k: v})
+    rec("lstm", g_weight_hh_l0=lstm.weight_hh_l0.grad, g_weight_ih_l1_reverse=lstm.weight_ih_l1_reverse.grad)
+    meta.append({"op": "lstm", "tag": "lstm", "specs": specs, "input_size": 32, "hidden_size": 64, "num_layers": 2,
+                 "bidirectional": True})
+
     # ---- gated feed-forward block through the reference's injection (last: it rewires torch for good) ----
     import torch.nn.functional as F
     specs = dict(s_mixed)

@@ -200,10 +200,35 @@ def test_layer_variants_match_reference(golden_layers2):
     assert {m["tag"] for m in meta} >= {"mm_aw", "mm_wa", "mm_bias", "addmm", "lin_nobp", "bmm_nobp", "lin_rounds",
                                         "mm_rounds", "conv2d", "conv1d_groups", "conv3d", "convT2d"}
     for m in meta:
-        if m["op"] == "ffn":
+        if m["op"] in ("ffn", "lstm"):
             continue
         for name, (got, want) in _run_layers2_case(m, z, "cpu", torch.float32).items():
             assert _same(got, want), (m["tag"], name)
+
+
+def run_lstm_case(m, z, dev, dtype):
+    sp = finalize_mx_specs(dict(m["specs"], custom_cuda=(dev != "cpu")))
+    lstm = mx.LSTM(m["input_size"], m["hidden_size"], num_layers=m["num_layers"], bidirectional=m["bidirectional"],
+                   mx_specs=sp)
+    lstm.load_state_dict({k[len("lstm_p_"):]: torch.tensor(z[k]) for k in z.files if k.startswith("lstm_p_")})
+    lstm = lstm.to(dev).to(dtype)
+    x = torch.tensor(z["lstm_x"]).to(dev, dtype).requires_grad_()
+    out, (hn, cn) = lstm(x)
+    out.backward(torch.tensor(z["lstm_go"]).to(dev, dtype))
+    return {"out": (out, z["lstm_out"]), "hn": (hn, z["lstm_hn"]), "cn": (cn, z["lstm_cn"]), "gx": (x.grad, z["lstm_gx"]),
+            "g_weight_hh_l0": (lstm.weight_hh_l0.grad, z["lstm_g_weight_hh_l0"]),
+            "g_weight_ih_l1_reverse": (lstm.weight_ih_l1_reverse.grad, z["lstm_g_weight_ih_l1_reverse"])}
+
+
+def test_lstm_matches_reference(golden_layers2):
+    """Two-layer bidirectional MX LSTM, forward and backward, against the reference's (CPU: exact)."""
+    meta, z = golden_layers2
+    m = [r for r in meta if r["op"] == "lstm"][0]
+    for name, (got, want) in run_lstm_case(m, z, "cpu", torch.float32).items():
+        assert _same(got, want), name
+    lstm = mx.LSTM(8, 8, mx_specs=finalize_mx_specs(dict(m["specs"])))
+    with pytest.raises(ValueError):
+        lstm(torch.nn.utils.rnn.pack_sequence([torch.zeros(3, 8), torch.zeros(2, 8)]))
 
 
 def test_ffn_via_inject_pyt_ops_matches_reference_on_cpu(golden_layers2):
