@@ -242,6 +242,9 @@ class TensorParallelFFN(torch.nn.Module):
         pg, pu, pd = self._weights_packed()
         h = quantize_elemwise_op(h, sp, round=sp["round_output"])
         px = _pack(h, af, sp, rnd, True)                               # local tokens
+        n_chunks = self._token_chunks(h.shape[0])
+        if n_chunks > 1 and not self._use_scatter(h.device):
+            return self._forward_pipelined(h, px, pg, pu, pd, n_chunks)
         xc, xs, xk = self._all_gather_rows(px.codes.reshape(-1, self.hidden)), \
             self._all_gather_rows(px.scales.view(-1, 512)).view(-1), px.container
         T = xc.shape[0]
@@ -279,6 +282,74 @@ class TensorParallelFFN(torch.nn.Module):
         else:
             out = self._down_chunked(ac, as_, ak, dc, ds, dk, T, Il, rows)
         out = quantize_elemwise_op(out, sp, round=sp["round_output"])
+        return out.to(h.dtype)
+
+    def _token_chunks(self, local_tokens):
+        """Token chunks of the pipelined forward: more than one only with several ranks, for whole
+        128-row groups per chunk; MXQ_TP_TOKEN_CHUNKS overrides (1 = off)."""
+        if self.world == 1:
+            return 1
+        want = int(os.environ.get("MXQ_TP_TOKEN_CHUNKS", "0")) or (4 if self.world >= 4 else 1)
+        while want > 1 and (local_tokens % (128 * want) != 0):
+            want -= 1
+        return max(want, 1)
+
+    def _forward_pipelined(self, h, px, pg, pu, pd, n_chunks):
+        """The forward pass cut into token chunks (chunk c = the c-th part of EVERY rank's tokens, so each
+        chunk's exchange is balanced): the all-gather of chunk c+1's packed input and the reduce-scatter of
+        chunk c's fp32 partial sums run on NCCL's stream under the GEMMs of the neighbouring chunks.  Every
+        output element sums the same per-rank partials as the unchunked pass."""
+        from . import _backend as be
+        sp = self.mx_specs
+        af = _fmt(sp["a_elem_format"])
+        rnd, out_rnd = sp["round_mx_output"], _MODE[sp["round_output"]]
+        bits = sp["bfloat"] if sp["bfloat"] >= 10 else 0
+        H, Il, W = self.hidden, self.cols[1] - self.cols[0], self.world
+        Tl = h.shape[0]
+        rc = Tl // n_chunks                                     # local rows per chunk (multiple of 128)
+        sf_per_chunk = (rc // 128) * ((H + 127) // 128) * 512   # scale bytes of one local chunk (contiguous)
+        codes = px.codes.reshape(Tl, H)
+        scales = px.scales.view(-1)
+        eb, mb, _, mn, _ = _get_format_params(af)
+        fused = fused_bf16_ok(sp, h) and Il % 32 == 0 and sp["round_output"] in ("nearest", "floor", "even")
+
+        def gather(c):
+            xc = torch.empty((W * rc, H), dtype=torch.uint8, device=h.device)
+            xs = torch.empty(W * sf_per_chunk, dtype=torch.uint8, device=h.device)
+            w1 = dist.all_gather_into_tensor(xc, codes[c * rc:(c + 1) * rc], group=self.group, async_op=True)
+            w2 = dist.all_gather_into_tensor(xs, scales[c * sf_per_chunk:(c + 1) * sf_per_chunk], group=self.group,
+                                             async_op=True)
+            return xc, xs, (w1, w2)
+
+        nxt = gather(0)
+        outs, works = [], []
+        for c in range(n_chunks):
+            xc, xs, ws = nxt
+            for w in ws:
+                w.wait()
+            if c + 1 < n_chunks:
+                nxt = gather(c + 1)
+            M = W * rc
+            gate = be.gemm_mx(xc, xs, pg.codes, pg.scales, 1, M, Il, H, px.container, pg.container, out_dtype=h.dtype,
+                              bfloat_bits=bits, round_mode=out_rnd)[0]
+            up = be.gemm_mx(xc, xs, pu.codes, pu.scales, 1, M, Il, H, px.container, pu.container, out_dtype=h.dtype,
+                            bfloat_bits=bits, round_mode=out_rnd)[0]
+            if fused:
+                ac, as_ = be.swiglu_quantize_mx(gate, up, sp["scale_bits"] or 8, eb, mb, mn, sp["mx_flush_fp32_subnorms"],
+                                                _MODE[rnd])
+                ak = 1 if eb == 5 else 0
+            else:
+                act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
+                pa = _pack(quantize_elemwise_op(act, sp, round=sp["round_output"]), af, sp, rnd, True)
+                ac, as_, ak = pa.codes, pa.scales, pa.container
+            part = be.gemm_mx(ac, as_, pd.codes, pd.scales, 1, M, H, Il, ak, pd.container, out_dtype=torch.float32,
+                              bfloat_bits=0, round_mode=-1)[0]
+            o = torch.empty((rc, H), dtype=torch.float32, device=h.device)
+            works.append(dist.reduce_scatter_tensor(o, part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            outs.append(o)
+        for w in works:
+            w.wait()
+        out = quantize_elemwise_op(torch.cat(outs, dim=0), sp, round=sp["round_output"])
         return out.to(h.dtype)
 
     def _down_chunked(self, ac, as_, ak, dc, ds, dk, T, Il, rows):

