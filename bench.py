@@ -406,10 +406,16 @@ def mx_ffn_block(torch, dist, dev, rank, world, T):
                 one.norm.bias.zero_()
             ref = one(torch.cat(xs, 0)).float()
             got = torch.cat(ys, 0).float()
-            ulp = ref.abs().clamp_min(1e-30) * 2.0 ** -7
+            # bf16 spacing at each output, and at the size of the outputs of its token: an output that is a
+            # near-cancelling sum of 28672 products legitimately moves by many of its own (tiny) ulps when the
+            # fp32 partial sums are added in another order
+            spacing = lambda t: torch.exp2(torch.floor(torch.log2(t.clamp_min(1e-30))) - 7)
+            row = ref.pow(2).mean(dim=1, keepdim=True).sqrt()
+            err = (got - ref).abs()
             res["numerics_vs_unsharded"] = {"tokens": n_chk * world,
-                                            "max_ulp": float(((got - ref).abs() / ulp).max().item()),
-                                            "frac_equal": float((got == ref).float().mean().item())}
+                                            "frac_equal": float((got == ref).float().mean().item()),
+                                            "max_ulp": float((err / spacing(ref.abs())).max().item()),
+                                            "max_ulp_at_token_scale": float((err / spacing(torch.maximum(ref.abs(), row))).max().item())}
             del one, wg, wu, wd
         dist.barrier()
     else:
@@ -675,7 +681,7 @@ def main():
                          "other_kernels": {
                              "mx_lastaxis_bf16_kernel": {"gbs": MX_PASS_BYTES / (last_ms * 1e-3) / 1e9,
                                                          "frac": MX_PASS_BYTES / (last_ms * 1e-3) / 1e9 / hbm},
-                             "ew_vec_kernel(fp32->bf16,even)": {"gbs": EW_PASS_BYTES / (group_ms[2] * 1e-3) / 1e9,
+                             "ew_f32_to_bf16_rne_kernel": {"gbs": EW_PASS_BYTES / (group_ms[2] * 1e-3) / 1e9,
                                                                 "frac": EW_PASS_BYTES / (group_ms[2] * 1e-3) / 1e9 / hbm}}},
             "e2e": {"value": world * STEP_BYTES / e2e_s / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},

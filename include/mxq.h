@@ -50,6 +50,10 @@ extern "C" {
 
 const char* mxq_status_string(int status);
 int mxq_version(void);
+/* Launches made by this process so far: what = 0 block-scaled GEMMs (through any entry point),
+ * what = 1 MX quantizations (mxq_quantize_mx and the fused packing entry points, the ones inside
+ * the composite linear calls included).  For tests and accounting; no reference counterpart. */
+int64_t mxq_launch_count(int what);
 
 /*
  * Device buffers shared between the processes of one node (no reference
@@ -304,6 +308,43 @@ int mxq_linear_fwd(const void* x, int x_dtype, int64_t M, int64_t K, int a_ebits
                    int out_bfloat_bits, int out_round, const void* bias, void* workspace,
                    int64_t workspace_bytes, void* stream);
 int64_t mxq_linear_workspace_bytes(int64_t M, int64_t K);
+
+/*
+ * One MX linear layer of a training step as two calls: forward with the weight
+ * quantized in the call (the reference does so on every forward,
+ * mx/linear.py:40-96), and both gradient products of LinearFunction.backward
+ * (mx/linear.py:103-200) at once.  Each call only chains this library's kernels on
+ * `stream` (MX packings + block-scaled GEMMs); the packed operands live in the
+ * caller's workspace of mxq_linear_train_workspace_bytes(M, K, N) bytes (256-byte
+ * aligned; its first 4 bytes are the call's status word: 0 or MXQ_ERR_DEVICE).
+ *   x [M, K], w [N, K], grad_out [M, N]: `dtype`, contiguous
+ *   mxq_elem_format: element format and MX rounding of one operand (float formats
+ *     with a one-byte container; round nearest / floor / even)
+ *   forward:  y = round(MX_a(x) MX_w(w)^T (+ bias)), blocks of 32 along K (K % 32 == 0)
+ *   backward: grad_w [N, K] = round(MX(go)^T MX(x)), blocks along the M tokens
+ *             (go_fmt_gw = a_elem_format_bp_ex, x_fmt_gw = a_elem_format_bp);
+ *             grad_x [M, K] = round(MX(go) MX(w)), blocks along N
+ *             (go_fmt_gi = a_elem_format_bp_os, w_fmt_gi = w_elem_format_bp);
+ *             M % 32 == 0, N % 32 == 0, K % 4 == 0; grad_x or grad_w may be NULL.
+ *   out_bfloat_bits and the round_* arguments: as in mxq_gemm_mx.
+ */
+typedef struct mxq_elem_format {
+    int ebits;
+    int mbits;
+    float max_norm;
+    int round;
+} mxq_elem_format;
+int64_t mxq_linear_train_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int mxq_linear_fwd_train(const void* x, const void* w, int dtype, int64_t M, int64_t K, int64_t N,
+                         const mxq_elem_format* a_fmt, const mxq_elem_format* w_fmt, int scale_bits,
+                         int flush_fp32_subnorms, void* y, int y_dtype, int out_bfloat_bits, int out_round,
+                         const void* bias, void* workspace, int64_t workspace_bytes, void* stream);
+int mxq_linear_bwd(const void* grad_out, const void* x, const void* w, int dtype, int64_t M, int64_t K, int64_t N,
+                   const mxq_elem_format* go_fmt_gw, const mxq_elem_format* x_fmt_gw,
+                   const mxq_elem_format* go_fmt_gi, const mxq_elem_format* w_fmt_gi, int scale_bits,
+                   int flush_fp32_subnorms, void* grad_x, void* grad_w, int g_dtype, int out_bfloat_bits,
+                   int round_grad_input, int round_grad_weight, void* workspace, int64_t workspace_bytes,
+                   void* stream);
 
 /*
  * mxq_linear_fwd for callers that cannot allocate and have no buffer to lend.

@@ -28,6 +28,11 @@ class MxqError(RuntimeError):
     pass
 
 
+class ElemFormatC(ctypes.Structure):
+    """struct mxq_elem_format of include/mxq.h"""
+    _fields_ = [("ebits", ctypes.c_int), ("mbits", ctypes.c_int), ("max_norm", ctypes.c_float), ("round", ctypes.c_int)]
+
+
 def lib():
     global _lib
     if _lib is None:
@@ -62,6 +67,12 @@ def lib():
                                           i32, i32, i32, vp]
         L.mxq_sum_slabs_f32.argtypes = [vp, i32, i64, vp, vp]
         L.mxq_rmsnorm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, f32, vp]
+        fp = ctypes.POINTER(ElemFormatC)
+        L.mxq_linear_train_workspace_bytes.argtypes = [i64, i64, i64]
+        L.mxq_linear_train_workspace_bytes.restype = i64
+        L.mxq_linear_fwd_train.argtypes = [vp, vp, i32, i64, i64, i64, fp, fp, i32, i32, vp, i32, i32, i32, vp, vp, i64, vp]
+        L.mxq_linear_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, fp, fp, fp, fp, i32, i32, vp, vp, i32, i32, i32, i32,
+                                     vp, i64, vp]
         L.mxq_cpu_quantize_mx.argtypes = [vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32, i32, i32, vp, i32]
         L.mxq_cpu_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, i32]
         _lib = L
@@ -391,6 +402,40 @@ def linear_fwd(x, w_codes, w_scales, w_fmt, a_ebits, a_mbits, a_max_norm, a_roun
     return y, workspace
 
 
+def linear_fwd_train(x, w, a_fmt, w_fmt, scale_bits, flush, out_dtype, bfloat_bits, out_round, bias=None):
+    """y = round(MX(x) MX(w)^T (+ bias)) with both operands quantized in the call; see mxq_linear_fwd_train.
+    x [M, K], w [N, K] contiguous CUDA tensors of one dtype; a_fmt / w_fmt: ElemFormatC."""
+    M, K = x.shape
+    N = w.shape[0]
+    L = lib()
+    ws = torch.empty(L.mxq_linear_train_workspace_bytes(M, K, N), dtype=torch.uint8, device=x.device)
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    with _device_of(x.device):
+        check(L.mxq_linear_fwd_train(_ptr(x), _ptr(w), _DT[x.dtype], M, K, N, ctypes.byref(a_fmt), ctypes.byref(w_fmt),
+                                     int(scale_bits), int(bool(flush)), _ptr(y), _DT[y.dtype], int(bfloat_bits),
+                                     int(out_round), _ptr(bias), _ptr(ws), ws.numel(), _stream(x)))
+    return y
+
+
+def linear_bwd(go, x, w, go_fmt_gw, x_fmt_gw, go_fmt_gi, w_fmt_gi, scale_bits, flush, out_dtype, bfloat_bits,
+               round_grad_input, round_grad_weight, want_gx=True, want_gw=True):
+    """(grad_x [M, K] or None, grad_w [N, K] or None) of an MX linear layer; see mxq_linear_bwd."""
+    M, N = go.shape
+    K = x.shape[1]
+    L = lib()
+    ws = torch.empty(L.mxq_linear_train_workspace_bytes(M, K, N), dtype=torch.uint8, device=go.device)
+    gx = torch.empty((M, K), dtype=out_dtype, device=go.device) if want_gx else None
+    gw = torch.empty((N, K), dtype=out_dtype, device=go.device) if want_gw else None
+    with _device_of(go.device):
+        check(L.mxq_linear_bwd(_ptr(go), _ptr(x), _ptr(w), _DT[go.dtype], M, K, N, ctypes.byref(go_fmt_gw),
+                               ctypes.byref(x_fmt_gw), ctypes.byref(go_fmt_gi), ctypes.byref(w_fmt_gi), int(scale_bits),
+                               int(bool(flush)), _ptr(gx), _ptr(gw), _DT[out_dtype], int(bfloat_bits),
+                               int(round_grad_input), int(round_grad_weight), _ptr(ws), ws.numel(), _stream(go)))
+    return gx, gw
+
+
 def _require_bf16(t, name):
     if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.bfloat16):
         raise MxqError("%s must be a contiguous bfloat16 CUDA tensor" % name)
@@ -480,6 +525,14 @@ def rmsnorm_bf16(x, weight, bias, eps, want_saved=False):
         check(lib().mxq_rmsnorm_bf16(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(xn), _ptr(ri), rows, hidden,
                                      float(eps), _stream(x)))
     return (out, xn, ri) if want_saved else out
+
+
+def launch_count(what):
+    """Launches made by this process: 0 = block-scaled GEMMs, 1 = MX quantizations; see mxq_launch_count."""
+    L = lib()
+    L.mxq_launch_count.restype = ctypes.c_int64
+    L.mxq_launch_count.argtypes = [ctypes.c_int]
+    return int(L.mxq_launch_count(int(what)))
 
 
 def device_status(clear=True):

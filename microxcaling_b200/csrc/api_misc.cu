@@ -14,7 +14,14 @@ extern "C" const char* mxq_status_string(int status) {
         default: return "unknown status";
     }
 }
-extern "C" int mxq_version(void) { return 1; }
+extern "C" int mxq_version(void) { return 2; }
+
+namespace mxq {
+std::atomic<int64_t> g_launch_count[2];
+}
+extern "C" int64_t mxq_launch_count(int what) {
+    return (what == 0 || what == 1) ? mxq::g_launch_count[what].load(std::memory_order_relaxed) : -1;
+}
 
 // ---------------------------------------------------------------------------
 // Receive buffers that other processes of the node can map (CUDA IPC).  The

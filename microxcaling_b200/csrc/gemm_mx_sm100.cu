@@ -766,6 +766,7 @@ int gemm_mx_with_status(const void* a_codes, const void* a_scales, const void* b
     g.rnd.even_on = (rounds && out_round == MXQ_ROUND_EVEN) ? 1u : 0u;
     g.rnd.add = !rounds ? 0u : (out_round == MXQ_ROUND_NEAREST ? (1u << (drop - 1)) : (out_round == MXQ_ROUND_EVEN ? (mask >> 1) : 0u));
     g.epi_kind = (out_dtype == MXQ_BF16 && rounds && drop == 16 && !bias) ? out_round : 3;
+    g_launch_count[0].fetch_add(1, std::memory_order_relaxed);
     CUtensorMap ta, tb;
     int rc = make_operand_map(&ta, a_codes, batch, M, K, kBM);
     if (rc) return rc;

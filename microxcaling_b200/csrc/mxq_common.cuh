@@ -29,6 +29,9 @@ inline int sm_count() {
     return n;
 }
 
+// Launch statistics of this process (mxq_launch_count): 0 = block-scaled GEMMs, 1 = MX quantizations.
+extern std::atomic<int64_t> g_launch_count[2];
+
 inline int check_launch() {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MXQ_OK : MXQ_ERR_CUDA;

@@ -174,6 +174,44 @@ ew_bf16_pairs_kernel(const EwArgs a, const int64_t nvec, const uint32_t drop16, 
     }
 }
 
+// fp32 -> bfloat16 storage, round to nearest even, subnormals kept, overflow to Inf: the cast
+// `A.to(torch.bfloat16)` the reference takes for bfloat = 16, round = 'even' (mx/elemwise_ops.py:248-251).
+// The hardware conversion is that rounding; NaN results are rewritten to the quiet NaN torch's cast
+// produces (0x7fc0).  A thread converts four groups of eight elements, all eight 16-byte loads issued
+// before the first use.
+constexpr int kCastUnroll = 4;
+__global__ void __launch_bounds__(kEwThreads)
+ew_f32_to_bf16_rne_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, const int64_t nvec) {
+    const int64_t base = (int64_t)blockIdx.x * (kEwThreads * kCastUnroll);
+    uint4 lo[kCastUnroll], hi[kCastUnroll];
+    bool live[kCastUnroll];
+#pragma unroll
+    for (int u = 0; u < kCastUnroll; ++u) {
+        const int64_t v = base + (int64_t)u * kEwThreads + threadIdx.x;
+        live[u] = v < nvec;
+        lo[u] = live[u] ? __ldg(in + 2 * v) : make_uint4(0, 0, 0, 0);
+        hi[u] = live[u] ? __ldg(in + 2 * v + 1) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kCastUnroll; ++u) {
+        if (!live[u]) continue;
+        const uint32_t f[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1]));
+            uint32_t p = *reinterpret_cast<const uint32_t*>(&h);
+            const uint32_t q = p & 0x7fff7fffu;
+            if (((q + 0x007f007fu) & 0x80008000u) != 0) {      // a half above 0x7f80: NaN
+                if ((q & 0xffffu) > 0x7f80u) p = (p & 0xffff0000u) | 0x7fc0u;
+                if ((q >> 16) > 0x7f80u) p = (p & 0x0000ffffu) | 0x7fc00000u;
+            }
+            w[i] = p;
+        }
+        out[base + (int64_t)u * kEwThreads + threadIdx.x] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 template <int MODE>
 static int launch_ew_bf16_pairs(const EwArgs& a, cudaStream_t st) {
     // bits = P + 1 with P significand bits; bf16 carries 8, so 8 - P low bits go
@@ -224,6 +262,17 @@ static int dispatch_path(const EwArgs& a, cudaStream_t st) {
             case RZ:      return launch_ew_bf16_pairs<RZ>(a, st);
             default:      return launch_ew_bf16_pairs<RN_EVEN>(a, st);
         }
+    }
+    if (IN_DT == DT_F32 && OUT_DT == DT_BF16 && a.exp_bits == 8 && a.bits == 9 && a.mode == RN_EVEN && a.allow_denorm &&
+        !a.saturate && a.max_bits == 0x7f7f0000u && aligned16(a.in) && aligned16(a.out) && a.n >= 8) {
+        const int64_t nvec = a.n / 8;
+        const int64_t tile = (int64_t)kEwThreads * kCastUnroll;
+        const int64_t grid = (nvec + tile - 1) / tile;
+        if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
+        ew_f32_to_bf16_rne_kernel<<<(unsigned)grid, kEwThreads, 0, st>>>(reinterpret_cast<const uint4*>(a.in),
+                                                                         reinterpret_cast<uint4*>(a.out), nvec);
+        if (nvec * 8 < a.n) ew_scalar_kernel<DT_F32, DT_BF16, 0, RN_EVEN><<<1, 128, 0, st>>>(a, nvec * 8, a.n);
+        return check_launch();
     }
     if (a.exp_bits == 8 && a.mode <= RN_EVEN) {
         switch (a.mode) {

@@ -43,6 +43,7 @@ extern "C" int mxq_quantize_mx(const void* in, void* out, void* codes, void* sca
     a.div_rpb.set((uint32_t)std::min<int64_t>(a.sf_rpb, 0xffffffffLL));
     a.fmt = make_fmt(elem_ebits, elem_mbits, elem_max_norm, rmode);
     set_fast_consts(a);
+    g_launch_count[1].fetch_add(1, std::memory_order_relaxed);
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case MXQ_F32: return dispatch_dt<DT_F32>(a, st);

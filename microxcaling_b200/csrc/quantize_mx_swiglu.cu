@@ -62,6 +62,7 @@ extern "C" int mxq_swiglu_quantize_mx(const void* gate, const void* up, void* co
     a.div_rpb.set((uint32_t)std::min<int64_t>(a.sf_rpb, 0xffffffffLL));
     a.fmt = make_fmt(elem_ebits, elem_mbits, elem_max_norm, rmode);
     set_fast_consts(a);
+    g_launch_count[1].fetch_add(1, std::memory_order_relaxed);
     const int64_t nvec = rows * K / 8;
     cudaStream_t st = (cudaStream_t)stream;
     switch (rmode) {

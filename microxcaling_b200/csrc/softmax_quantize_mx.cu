@@ -260,6 +260,7 @@ extern "C" int mxq_softmax_quantize_mx(const void* x, void* probs, void* codes, 
     a.div_rpb.set((uint32_t)std::min<int64_t>(a.sf_rpb, 0xffffffffLL));
     a.fmt = make_fmt(elem_ebits, elem_mbits, elem_max_norm, rmode);
     set_fast_consts(a);
+    g_launch_count[1].fetch_add(1, std::memory_order_relaxed);
     const uint16_t* table = exp_table();
     if (!table) return MXQ_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;

@@ -16,6 +16,30 @@ from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
 
 f_linear = F.linear
 torch_matmul = torch.matmul
+_MODE = {"nearest": 0, "floor": 1, "even": 2}
+
+
+def _cfmt(fmt, rnd):
+    """ElemFormatC of an element format name and MX rounding mode, or None when the format has no
+    one-byte float container or the mode is not a kernel mode."""
+    from . import _backend
+    from ._mxgemm import _fmt
+    from .formats import _get_format_params
+    if fmt is None or rnd not in _MODE:
+        return None
+    ebits, mbits, _, max_norm, _ = _get_format_params(_fmt(fmt))
+    if ebits == 0 or mbits > 5:
+        return None
+    return _backend.ElemFormatC(ebits, mbits, max_norm, _MODE[rnd])
+
+
+def _one_call_ok(a, b, sp, out_round):
+    """Both tensors CUDA, contiguous-izable, same kernel dtype; block 32, max-exponent scales, bfloat output."""
+    if not (a.is_cuda and b.is_cuda) or a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    if sp["block_size"] != 32 or sp["shared_exp_method"] != "max" or sp["fp"] > 0 or 0 < sp["bfloat"] < 10:
+        return False
+    return out_round in _MODE and a.numel() > 0 and b.numel() > 0
 
 
 class LinearFunction(torch.autograd.Function):
@@ -42,6 +66,21 @@ class LinearFunction(torch.autograd.Function):
             ctx.save_for_backward(input, weight)
         if bf_weight.dtype != bf_in.dtype:
             bf_weight = bf_weight.to(bf_in.dtype)
+        K = bf_in.shape[-1]
+        fa = _cfmt(mx_specs["a_elem_format"], mx_specs["round_mx_output"])
+        fw = _cfmt(mx_specs["w_elem_format"], mx_specs["round_mx_output"])
+        if packed_weight is None and fa is not None and fw is not None and K % 32 == 0 and bf_in.dim() >= 2 and \
+                _one_call_ok(bf_in, bf_weight, mx_specs, mx_specs["round_output"]):
+            # quantize both operands and multiply in one library call
+            from . import _backend
+            y = _backend.linear_fwd_train(bf_in.reshape(-1, K).contiguous(), bf_weight.contiguous(), fa, fw,
+                                          mx_specs["scale_bits"] or 8, mx_specs["mx_flush_fp32_subnorms"], bf_in.dtype,
+                                          mx_specs["bfloat"] if mx_specs["bfloat"] >= 10 else 0,
+                                          _MODE[mx_specs["round_output"]], bf_bias)
+            ctx.mx_specs = get_backwards_mx_specs(mx_specs)
+            ctx.prequantized_weights = prequantized_weights
+            ctx.name = name
+            return y.reshape(*bf_in.shape[:-1], weight.shape[0])
         output = mx_gemm(bf_in, bf_weight, mx_specs["a_elem_format"], mx_specs["w_elem_format"], mx_specs,
                          mx_specs["round_mx_output"], mx_specs["round_mx_output"], mx_specs["round_output"],
                          bias=bf_bias, trans2=True, in2_packed=packed_weight)
@@ -57,6 +96,30 @@ class LinearFunction(torch.autograd.Function):
         sp = ctx.mx_specs
         out_dim, in_dim = weight.shape
         grad_output = quantize_elemwise_op(grad_output, mx_specs=sp, round=sp["round_grad_input"])
+
+        # both gradient products in one library call where the formats and shapes allow it
+        flat_ok = input.dim() == 2 or (input.dim() > 2 and sp["block_size"] and input.shape[-2] % sp["block_size"] == 0)
+        M = grad_output.numel() // out_dim if out_dim else 0
+        f_gw = (_cfmt(sp["a_elem_format_bp_ex"], sp["round_mx_grad_output_grad_weight"]),
+                _cfmt(sp["a_elem_format_bp"], sp["round_mx_input_grad_weight"]))
+        f_gi = (_cfmt(sp["a_elem_format_bp_os"], sp["round_mx_grad_output_grad_input"]),
+                _cfmt(sp["w_elem_format_bp"], sp["round_mx_weight_grad_input"]))
+        if flat_ok and None not in f_gw and None not in f_gi and M % 32 == 0 and out_dim % 32 == 0 and in_dim % 4 == 0 \
+                and sp["round_grad_input"] in _MODE and sp["round_grad_weight"] in _MODE \
+                and _one_call_ok(grad_output, input, sp, sp["round_grad_input"]) and weight.is_cuda:
+            from . import _backend
+            w = weight if weight.dtype == grad_output.dtype else weight.to(grad_output.dtype)
+            gx, gw = _backend.linear_bwd(grad_output.reshape(M, out_dim).contiguous(), input.reshape(M, in_dim).contiguous(),
+                                         w.contiguous(), f_gw[0], f_gw[1], f_gi[0], f_gi[1], sp["scale_bits"] or 8,
+                                         sp["mx_flush_fp32_subnorms"], grad_output.dtype,
+                                         sp["bfloat"] if sp["bfloat"] >= 10 else 0, _MODE[sp["round_grad_input"]],
+                                         _MODE[sp["round_grad_weight"]], want_gx=ctx.needs_input_grad[0],
+                                         want_gw=ctx.needs_input_grad[1])
+            grad_bias = None
+            if ctx.has_bias:
+                grad_bias = quantize_elemwise_op(grad_output.reshape(-1, out_dim).sum(0), mx_specs=sp,
+                                                 round=sp["round_grad_weight"])
+            return (gx.reshape(input.shape) if gx is not None else None, gw, grad_bias, None, None, None, None)
 
         # grad_weight [out, in] = g^T x, blocks along the token axis.  A 3-D input
         # blocks along its own sequence axis; that equals blocking the flattened

@@ -165,8 +165,10 @@ def test_config5_ffn_via_inject_pyt_ops_full_size(monkeypatch):
     torch.manual_seed(0)
     blk = _build_injected_ffn(H, I, sp, "cuda").eval()
     gemms = []
-    real = _backend.gemm_mx
-    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (gemms.append((a[5], a[6], a[7])), real(*a, **k))[1])
+    real = _backend.linear_fwd_train
+    monkeypatch.setattr(_backend, "linear_fwd_train", lambda x_, w_, *a, **k: (gemms.append((x_.shape[0], w_.shape[0], x_.shape[1])),
+                                                                                real(x_, w_, *a, **k))[1])
+    g0 = _backend.launch_count(0)
     seen = {}
     hooks = [m.register_forward_hook(lambda mod, inp, out, n=n: seen.__setitem__(n, (inp[0], out)))
              for n, m in (("gate", blk.gate), ("up", blk.up), ("down", blk.down), ("norm", blk.norm))]
@@ -178,7 +180,8 @@ def test_config5_ffn_via_inject_pyt_ops_full_size(monkeypatch):
     for h_ in hooks:
         h_.remove()
     assert _backend.device_status() == 0
-    assert gemms == [(T, I, H), (T, I, H), (T, H, I)], gemms          # (M, N, K) of the three tensor-core products
+    assert gemms == [(T, I, H), (T, I, H), (T, H, I)], gemms          # (M, N, K) of the three linear layers
+    assert _backend.launch_count(0) - g0 == 3                          # each one block-scaled tensor-core GEMM
     assert y.shape == (4, 4096, H) and y.dtype == torch.bfloat16
     rng = np.random.default_rng(5)
     ti = lambda a: torch.as_tensor(a, device="cuda")
@@ -234,9 +237,6 @@ def test_ffn_via_inject_pyt_ops_matches_reference_fixture(golden_layers2, monkey
     with torch.no_grad():
         blk.norm.weight.copy_(t("norm_w")); blk.norm.bias.copy_(t("norm_b"))
         blk.gate.weight.copy_(t("wg")); blk.up.weight.copy_(t("wu")); blk.down.weight.copy_(t("wd"))
-    calls = []
-    real = _backend.gemm_mx
-    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
     bf = dtype == torch.bfloat16
 
     def close(got, name, key, max_ulp=1, min_exact=0.97):
@@ -258,7 +258,7 @@ def test_ffn_via_inject_pyt_ops_matches_reference_fixture(golden_layers2, monkey
         close(blk.up(t("h")), "up", "up")
         close(torch.mul(F.silu(t("gate")), t("up")), "act", "act", max_ulp=8 if bf else 1, min_exact=0.75 if bf else 0.999)
         close(blk.down(t("act")), "down", "y")
-        n0 = len(calls)
+        n0 = _backend.launch_count(0)
         # end to end the stages' one-ulp differences travel on: every output is a sum over the intermediate
         # features, so the bound is relative to the size of the outputs of its token, not to the output itself
         yb = blk(t("x")).float().cpu().numpy().astype(np.float64)
@@ -267,4 +267,4 @@ def test_ffn_via_inject_pyt_ops_matches_reference_fixture(golden_layers2, monkey
         bound = 2.0 ** -3 if bf else 2.0 ** -5            # bfloat16 storage: the tie differences of every stage add up
         assert (np.abs(yb - yr) <= bound * (np.abs(yr) + row)).all(), float((np.abs(yb - yr) / (np.abs(yr) + row)).max())
         assert float((yb == yr).mean()) >= (0.1 if bf else 0.6)
-        assert len(calls) - n0 == 3
+        assert _backend.launch_count(0) - n0 == 3

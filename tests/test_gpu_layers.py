@@ -67,16 +67,15 @@ def test_layers_match_reference(golden_layers, dtype):
 def test_fast_path_is_taken(monkeypatch):
     """FP8/FP6/FP4 formats with block 32 and K % 128 == 0 must reach the tensor-core GEMM."""
     from microxcaling_b200 import _backend
-    calls = []
-    real = _backend.gemm_mx
-    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: calls.append(1) or real(*a, **k))
     sp = finalize_mx_specs({"w_elem_format": "fp4_e2m1", "a_elem_format": "fp8_e4m3", "block_size": 32,
                             "bfloat": 16, "custom_cuda": True})
     x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     lin = mx.Linear(512, 384, bias=True, mx_specs=sp).cuda().to(torch.bfloat16)
+    g0, q0 = _backend.launch_count(0), _backend.launch_count(1)
     y = lin(x)
     y.backward(torch.randn_like(y))
-    assert len(calls) == 3                      # forward, grad_weight, grad_input
+    assert _backend.launch_count(0) - g0 == 3   # forward, grad_weight, grad_input on the tensor cores
+    assert _backend.launch_count(1) - q0 == 6   # two MX packings per product
     assert _backend.device_status() == 0
 
 
@@ -144,27 +143,25 @@ def test_weight_is_requantized_every_call_unless_frozen(monkeypatch, tmp_path):
                             "round": "even"})
     lin = mx.Linear(256, 128, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
     x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
-    calls = []
-    real = _backend.quantize_mx
-    monkeypatch.setattr(_backend, "quantize_mx", lambda A, *a, **k: (calls.append(tuple(A.shape)), real(A, *a, **k))[1])
+    packs = lambda: _backend.launch_count(1)
     with torch.no_grad():
         y1 = lin(x)
         lin.weight.data.mul_(2.0)                   # invisible to data_ptr / _version
-        n = len(calls)
+        n = packs()
         y2 = lin(x)
-        assert len(calls) - n == 2                  # activations and weight packed again
+        assert packs() - n == 2                     # activations and weight packed again
         assert torch.equal(y2.float(), 2.0 * y1.float())
         lin.eval()
         lin.prequantize_weights()
         y3 = lin(x)
-        n = len(calls)
+        n = packs()
         y4 = lin(x)
-        assert len(calls) - n == 1                  # only the activations
+        assert packs() - n == 1                     # only the activations
         assert torch.equal(y3, y4) and torch.equal(y3, y2)
         lin.weight.mul_(0.5)                        # a tracked in-place update: the packed weight follows
-        n = len(calls)
+        n = packs()
         y5 = lin(x)
-        assert len(calls) - n == 2 and torch.equal(y5, y1)
+        assert packs() - n == 2 and torch.equal(y5, y1)
         # file round trip of the packed weight, used in place of the tensor
         pw = lin.packed_weight()
         path = str(tmp_path / "w.mxq")
@@ -187,15 +184,17 @@ def test_linear_with_odd_feature_count_takes_the_tensor_core_path(monkeypatch):
     torch.manual_seed(0)
     lin = mx.Linear(96, 160, bias=False, mx_specs=sp).cuda().to(torch.bfloat16)
     x = torch.randn(200, 96, device="cuda", dtype=torch.bfloat16)
-    calls = []
-    real = _backend.gemm_mx
-    monkeypatch.setattr(_backend, "gemm_mx", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    g0 = _backend.launch_count(0)
     with torch.no_grad():
         got = lin(x)
-    assert calls
+    assert _backend.launch_count(0) - g0 == 1
+    import importlib
+    linear_mod = importlib.import_module("microxcaling_b200.linear")
     monkeypatch.setattr(_mxgemm, "_fast_ok", lambda *a, **k: False)
+    monkeypatch.setattr(linear_mod, "_one_call_ok", lambda *a, **k: False)
     with torch.no_grad():
         want = lin(x)
+    assert _backend.launch_count(0) - g0 == 1
     close_bf16(got, want.float().cpu().numpy(), "linear K=96")
 
 
@@ -271,14 +270,11 @@ def test_lstm_matches_reference_on_gpu(golden_layers2):
     from microxcaling_b200 import _backend
     meta, z = golden_layers2
     m = [r for r in meta if r["op"] == "lstm"][0]
-    calls = []
-    real = _backend.gemm_mx
-    _backend.gemm_mx = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
-    try:
-        res = run_lstm_case(m, z, "cuda", torch.float32)
-    finally:
-        _backend.gemm_mx = real
-    assert len(calls) >= 3 * (4 + 4 * 5)            # per direction and layer: 1 input + 5 hidden products, x3 with backward
+    g0 = _backend.launch_count(0)
+    res = run_lstm_case(m, z, "cuda", torch.float32)
+    # per direction and layer: 1 input + 5 hidden products forward, two gradient products each backward,
+    # less the gradient with respect to the initial hidden state (not needed) of each direction and layer
+    assert _backend.launch_count(0) - g0 == 3 * (4 + 4 * 5) - 4
     for name, (got, want) in res.items():
         a, b = got.detach().float().cpu().numpy().astype(np.float64), want.astype(np.float64)
         scale = np.sqrt((b ** 2).mean())
