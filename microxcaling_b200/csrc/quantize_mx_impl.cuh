@@ -643,16 +643,20 @@ __global__ void __launch_bounds__(kStrBfThreads, (CK == CK_NONE && !TRANSPOSED) 
 mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nbgrp) {
     constexpr int kBlocksPerThread = TRANSPOSED ? 4 : 1;
     __shared__ uint4 stage[TRANSPOSED ? kStrBfThreads * 4 * 4 : 1];
+    // Columns are numbered across the leading axis: g = p * post + col.  A CTA owns 512 consecutive such
+    // columns (four per thread; post % 4 == 0 keeps a thread's four inside one p), so tensors whose `post` is
+    // short (the 128-wide heads of an attention block) still fill every thread.
     const int tid = threadIdx.x;
     const int64_t t = blockIdx.x;
     const int64_t ct = t % col_tiles;
-    const int64_t pb = t / col_tiles;
-    const int64_t bg = pb % nbgrp;
-    const int64_t p = pb / nbgrp;
-    const int64_t col0 = ct * (kStrBfThreads * 4);
-    const int64_t col = col0 + (int64_t)tid * 4;
-    const bool active = col < a.post;
+    const int64_t bg = t / col_tiles;
+    const int64_t g0 = ct * (kStrBfThreads * 4);
+    const int64_t gcol = g0 + (int64_t)tid * 4;
+    const int64_t gcols = a.pre * a.post;
+    const bool active = gcol < gcols;
     if (!TRANSPOSED && !active) return;
+    const int64_t p = active ? gcol / a.post : 0;
+    const int64_t col = active ? gcol - p * a.post : 0;
     const uint16_t* in = reinterpret_cast<const uint16_t*>(a.in);
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
     const int64_t padded = a.nblk * a.block;
@@ -777,8 +781,8 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             for (int it = 0; it < 16; ++it) {
                 const int id = it * kStrBfThreads + tid;
                 const int c = id >> 2, j = id & 3;
-                if (col0 + c < a.post && j < nchunk)
-                    *reinterpret_cast<uint4*>(a.codes + (p * a.post + col0 + c) * padded + k0 + j * 16) =
+                if (g0 + c < gcols && j < nchunk)
+                    *reinterpret_cast<uint4*>(a.codes + (g0 + c) * padded + k0 + j * 16) =
                         stage[id ^ ((id >> 4) & 7)];
             }
             __syncthreads();
@@ -881,9 +885,9 @@ static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream
 
 template <int MODE, bool WANT_DQ, int CK, bool TR>
 static int launch_strided_bf16_one(const MxArgs& a, cudaStream_t st) {
-    const int64_t col_tiles = (a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
+    const int64_t col_tiles = (a.pre * a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
     const int64_t nbgrp = TR ? (a.nblk + 3) / 4 : a.nblk;
-    const int64_t grid = col_tiles * a.pre * nbgrp;
+    const int64_t grid = col_tiles * nbgrp;
     if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;
     mx_strided_bf16_kernel<MODE, WANT_DQ, CK, TR><<<(unsigned)grid, kStrBfThreads, 0, st>>>(a, col_tiles, nbgrp);
     return check_launch();

@@ -156,16 +156,33 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
     // rows of up to kNormKeep * 256 vectors stay in registers between the two passes (one read of x)
     constexpr int kNormKeep = 4;
     const bool keep = vec && hidden / 8 <= (int64_t)kNormKeep * kNormThreads;
+    // `keep` rows are software-pipelined: the next row's loads are issued before the block-wide reduction of
+    // the current one, so they are in flight during the reduction, the normalisation and the stores
+    uint4 kept[kNormKeep], nxt[kNormKeep];
+    if (keep && (int64_t)blockIdx.x < rows) {
+        const uint4* xv = reinterpret_cast<const uint4*>(x + (int64_t)blockIdx.x * hidden);
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
+            nxt[k] = i < hidden / 8 ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
+        }
+    }
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint16_t* xr = x + row * hidden;
         float acc = 0.f;
-        uint4 kept[kNormKeep];
         if (keep) {
-            const uint4* xv = reinterpret_cast<const uint4*>(xr);
+#pragma unroll
+            for (int k = 0; k < kNormKeep; ++k) kept[k] = nxt[k];
+            if (row + gridDim.x < rows) {
+                const uint4* xn = reinterpret_cast<const uint4*>(x + (row + gridDim.x) * hidden);
+#pragma unroll
+                for (int k = 0; k < kNormKeep; ++k) {
+                    const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
+                    nxt[k] = i < hidden / 8 ? __ldg(xn + i) : make_uint4(0, 0, 0, 0);
+                }
+            }
 #pragma unroll
             for (int k = 0; k < kNormKeep; ++k) {
-                const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
-                kept[k] = i < hidden / 8 ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
                 const uint32_t q[4] = {kept[k].x, kept[k].y, kept[k].z, kept[k].w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
