@@ -55,6 +55,12 @@ int mxq_version(void);
  * the composite linear calls included).  For tests and accounting; no reference counterpart. */
 int64_t mxq_launch_count(int what);
 
+/* SMs the persistent GEMM kernels of this process occupy from the next launch on: sms > 0 sets the
+ * budget (values at or above the device's SM count mean all of them), 0 restores "all", a negative
+ * value only reads.  Returns the previous setting.  A caller that runs a collective beside a GEMM
+ * leaves the collective's CTAs room this way; results do not depend on it.  No reference counterpart. */
+int mxq_gemm_sm_budget(int sms);
+
 /*
  * Device buffers shared between the processes of one node (no reference
  * counterpart), the destinations of mxq_gemm_mx_scatter.  mxq_peer_alloc

@@ -8,6 +8,7 @@ tensors: if the library is missing, loading raises.
 ``funcs`` keeps the seven names the reference's pybind module exports
 (mx/cpp/funcs.cpp:234-242) so reference-style callers keep working.
 """
+import contextlib
 import ctypes
 import os
 
@@ -533,6 +534,17 @@ def launch_count(what):
     L.mxq_launch_count.restype = ctypes.c_int64
     L.mxq_launch_count.argtypes = [ctypes.c_int]
     return int(L.mxq_launch_count(int(what)))
+
+
+@contextlib.contextmanager
+def gemm_sm_budget(sms):
+    """Within the block the persistent GEMM kernels occupy at most `sms` SMs (0 = all), which leaves a
+    collective running beside them CTAs to run on; see mxq_gemm_sm_budget."""
+    prev = lib().mxq_gemm_sm_budget(int(sms))
+    try:
+        yield
+    finally:
+        lib().mxq_gemm_sm_budget(int(prev))
 
 
 def device_status(clear=True):

@@ -18,6 +18,11 @@ extern "C" int mxq_version(void) { return 2; }
 
 namespace mxq {
 std::atomic<int64_t> g_launch_count[2];
+std::atomic<int> g_gemm_sm_budget{0};
+}
+extern "C" int mxq_gemm_sm_budget(int sms) {
+    if (sms < 0) return mxq::g_gemm_sm_budget.load(std::memory_order_relaxed);
+    return mxq::g_gemm_sm_budget.exchange(sms, std::memory_order_relaxed);
 }
 extern "C" int64_t mxq_launch_count(int what) {
     return (what == 0 || what == 1) ? mxq::g_launch_count[what].load(std::memory_order_relaxed) : -1;

@@ -680,7 +680,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
         return MXQ_ERR_CUDA;
     const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
-    const int pairs = (int)std::min<int64_t>(tiles, sm_count() / 2);
+    const int pairs = (int)std::min<int64_t>(tiles, std::max(gemm_sms() / 2, 1));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(kGemmThreads);
@@ -704,7 +704,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMa
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess)
         return MXQ_ERR_CUDA;
     const int64_t tiles = g.m_tiles * g.n_tiles * g.batch;
-    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    const int grid = (int)std::min<int64_t>(tiles, gemm_sms());
     kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, tc, g);
     return check_launch();
 }

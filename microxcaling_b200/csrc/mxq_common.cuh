@@ -29,6 +29,13 @@ inline int sm_count() {
     return n;
 }
 
+// SMs the persistent GEMM kernels may occupy (mxq_gemm_sm_budget); 0 = every SM of the device.
+extern std::atomic<int> g_gemm_sm_budget;
+inline int gemm_sms() {
+    const int all = sm_count(), b = g_gemm_sm_budget.load(std::memory_order_relaxed);
+    return (b > 0 && b < all) ? b : all;
+}
+
 // Launch statistics of this process (mxq_launch_count): 0 = block-scaled GEMMs, 1 = MX quantizations.
 extern std::atomic<int64_t> g_launch_count[2];
 

@@ -214,6 +214,27 @@ __device__ __forceinline__ uint32_t encode2_e5m2(float lo, float hi) {
     asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// Two values rounded to a 6- or 4-bit element format by the hardware conversion (nearest-even on the
+// format's grid, subnormals included, saturating at its largest value), then widened to e4m3 code bytes;
+// the two widening conversions are exact because every value of the narrow formats is an e4m3 value.
+__device__ __forceinline__ uint32_t encode2_via_e3m2(float lo, float hi) {
+    uint16_t r;
+    asm("{\n\t.reg .b16 t;\n\t.reg .b32 f;\n\tcvt.rn.satfinite.e3m2x2.f32 t, %1, %2;\n\tcvt.rn.f16x2.e3m2x2 f, t;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 %0, f;\n\t}" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t encode2_via_e2m3(float lo, float hi) {
+    uint16_t r;
+    asm("{\n\t.reg .b16 t;\n\t.reg .b32 f;\n\tcvt.rn.satfinite.e2m3x2.f32 t, %1, %2;\n\tcvt.rn.f16x2.e2m3x2 f, t;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 %0, f;\n\t}" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t encode2_via_e2m1(float lo, float hi) {
+    uint16_t r;
+    asm("{\n\t.reg .b8 t;\n\t.reg .b32 f;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.rn.f16x2.e2m1x2 f, t;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 %0, f;\n\t}" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 __device__ __forceinline__ uint32_t encode1(float q, int ebits, int mbits) {
     if (ebits == 0) return (uint32_t)(__float2int_rn(ldexpf(q, mbits - 2)) & 0xff);
     return (ebits == 5 ? encode2_e5m2(q, 0.f) : encode2_e4m3(q, 0.f)) & 0xffu;

@@ -67,7 +67,8 @@ struct MxArgs {
     uint32_t fp_cmin_base;         // bits of cmin   = fp_cmin_base + (E << 23)
     uint32_t fp_maxn_base;         // bits of maxn   = fp_maxn_base + (E << 23)
     uint32_t fp_mp_base;           // packed bf16 maxn pair = fp_mp_base + E * 0x00800080
-    int direct8;                   // element format IS the code container (fp8_e4m3 / fp8_e5m2): see code_pair_direct
+    int direct;                    // element rounding by hardware conversion (see code_quad_direct): 0 no, 1 the format is its
+                                   // own container (fp8_e4m3 / fp8_e5m2), 2 fp6_e3m2, 3 fp6_e2m3, 4 fp4_e2m1 (e4m3 container)
 };
 
 // The unscaled fast path needs its per-block constants to be normal, finite
@@ -91,8 +92,8 @@ __host__ inline void set_fast_consts(MxArgs& a) {
     a.fp_cmin_base = ((uint32_t)(emin_f + kf_f) << 23) - (127u << 23);
     a.fp_maxn_base = mn - (127u << 23);
     a.fp_mp_base = (uint32_t)(mp_half < 0 ? 0 : mp_half) * 0x10001u;
-    a.direct8 = (a.fmt.ebits == 4 && a.fmt.mbits == 5 && a.fmt.max_norm == 448.0f) ||
-                (a.fmt.ebits == 5 && a.fmt.mbits == 4 && a.fmt.max_norm == 57344.0f);
+    const auto is = [&](int e, int m, float mx) { return a.fmt.ebits == e && a.fmt.mbits == m && a.fmt.max_norm == mx; };
+    a.direct = (is(4, 5, 448.0f) || is(5, 4, 57344.0f)) ? 1 : is(3, 4, 28.0f) ? 2 : is(2, 5, 7.5f) ? 3 : is(2, 3, 6.0f) ? 4 : 0;
 }
 
 // Last-axis kernels: byte index of the scale of linear block index `blk`
@@ -399,7 +400,9 @@ __device__ __forceinline__ uint32_t quant_pair_bf16(uint32_t w, float cmin_lo, f
 
 // Code container of the packed operand, fixed at compile time in the bf16
 // kernels so that only one conversion is emitted.
-enum : int { CK_NONE = 0, CK_E4M3 = 1, CK_E5M2 = 2 };
+// CK_E4M3N: e4m3 container of a narrower element format (fp6 / fp4) whose rounding the hardware
+// conversions do (MxArgs::direct says which); only the packing-only kernels are built with it.
+enum : int { CK_NONE = 0, CK_E4M3 = 1, CK_E5M2 = 2, CK_E4M3N = 3 };
 
 // two scaled magnitudes + the signs of the source pair w -> two code bytes (lo element in bits 0..7)
 template <int CK>
@@ -417,21 +420,34 @@ __device__ __forceinline__ uint32_t code_quad(float q0, float q1, float q2, floa
     return __byte_perm(lo, hi, 0x5410) | (__byte_perm(w01, w23, 0x7531) & 0x80808080u);
 }
 
-// Codes straight from the hardware conversion, for the two formats that ARE their container (fp8_e4m3,
-// fp8_e5m2) when only the packed operand is wanted: cvt.rn.satfinite rounds the scaled value to the
-// format's grid (subnormals included) to nearest-even and saturates at max_norm, which is the element
-// rounding of MX in 'even' mode; for 'nearest' (ties away from zero) the scale factor carries a relative
+// Codes straight from the hardware conversion when only the packed operand is wanted, for the formats
+// the conversion instructions know (fp8_e4m3 and fp8_e5m2, which are their own container; fp6_e3m2,
+// fp6_e2m3 and fp4_e2m1, narrowed and then widened exactly to an e4m3 byte): cvt.rn.satfinite rounds
+// the scaled value to the format's grid (subnormals included) to nearest-even and saturates at max_norm,
+// which is the element rounding of MX in 'even' mode; for 'nearest' (ties away from zero) the scale factor carries a relative
 // nudge of 2^-12, which turns every exact tie into a round-up and moves nothing else (a bfloat16 source
 // has 8 significant bits, so x / spacing is never within 2^-8 of a half-way point without being on it).
 // c = 2^-s (exact reciprocal of the block scale) or 2^-s * (1 + 2^-12); the products are exact in fp32
 // (8 x 13 significant bits).  The sign travels through the conversion.  Two pairs -> four code bytes.
 template <int CK>
-__device__ __forceinline__ uint32_t code_quad_direct(uint32_t w01, uint32_t w23, float c0, float c1, float c2, float c3) {
+__device__ __forceinline__ uint32_t direct_pair(float lo, float hi, int kind) {
+    if (CK == CK_E5M2) return encode2_e5m2(lo, hi);
+    if (CK != CK_E4M3N) return encode2_e4m3(lo, hi);
+    if (kind == 2) return encode2_via_e3m2(lo, hi);
+    return kind == 3 ? encode2_via_e2m3(lo, hi) : encode2_via_e2m1(lo, hi);
+}
+template <int CK>
+__device__ __forceinline__ uint32_t code_quad_direct(uint32_t w01, uint32_t w23, float c0, float c1, float c2, float c3,
+                                                     int kind) {
     const float v0 = __uint_as_float(w01 << 16) * c0, v1 = __uint_as_float(w01 & 0xffff0000u) * c1;
     const float v2 = __uint_as_float(w23 << 16) * c2, v3 = __uint_as_float(w23 & 0xffff0000u) * c3;
-    const uint32_t lo = CK == CK_E5M2 ? encode2_e5m2(v0, v1) : encode2_e4m3(v0, v1);
-    const uint32_t hi = CK == CK_E5M2 ? encode2_e5m2(v2, v3) : encode2_e4m3(v2, v3);
-    return __byte_perm(lo, hi, 0x5410);
+    return __byte_perm(direct_pair<CK>(v0, v1, kind), direct_pair<CK>(v2, v3, kind), 0x5410);
+}
+// whether a kernel built for container CK rounds its elements with the conversions
+template <bool WANT_DQ, int CK, int MODE>
+__device__ __forceinline__ bool use_direct(const MxArgs& a) {
+    if (WANT_DQ || CK == CK_NONE || MODE == RZ) return false;
+    return CK == CK_E4M3N ? true : a.direct == 1;
 }
 // the factor c of a block: bits of 2^-s with the 2^-12 nudge in the mantissa for half-away rounding
 template <int MODE>
@@ -569,11 +585,11 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
             }
             continue;
         }
-        if (!WANT_DQ && CK != CK_NONE && MODE != RZ && a.direct8) {
+        if (use_direct<WANT_DQ, CK, MODE>(a)) {
             if (live[u]) {
                 const float cf = direct_factor<MODE>(fb.inv);
-                reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(code_quad_direct<CK>(w[0], w[1], cf, cf, cf, cf),
-                                                                   code_quad_direct<CK>(w[2], w[3], cf, cf, cf, cf));
+                reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(code_quad_direct<CK>(w[0], w[1], cf, cf, cf, cf, a.direct),
+                                                                   code_quad_direct<CK>(w[2], w[3], cf, cf, cf, cf, a.direct));
             }
             continue;
         }
@@ -722,7 +738,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             } else {
                 const uint32_t mp0 = a.fp_mp_base + ((fb[0].E | (fb[1].E << 16)) << 7);
                 const uint32_t mp1 = a.fp_mp_base + ((fb[2].E | (fb[3].E << 16)) << 7);
-                const bool direct = !WANT_DQ && CK != CK_NONE && MODE != RZ && a.direct8;
+                const bool direct = use_direct<WANT_DQ, CK, MODE>(a);
                 float inv[4] = {fb[0].inv, fb[1].inv, fb[2].inv, fb[3].inv};
                 if (direct) {
 #pragma unroll
@@ -736,7 +752,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
                     for (int rr = 0; rr < 4; ++rr) {
                         const int r = r4 * 4 + rr;
                         if (!WANT_DQ && CK != CK_NONE && MODE != RZ && direct) {
-                            c4[rr] = code_quad_direct<CK>(raw[r].x, raw[r].y, inv[0], inv[1], inv[2], inv[3]);
+                            c4[rr] = code_quad_direct<CK>(raw[r].x, raw[r].y, inv[0], inv[1], inv[2], inv[3], a.direct);
                             if (!TRANSPOSED)
                                 *reinterpret_cast<uint32_t*>(a.codes + base + (int64_t)r * a.post) = c4[rr];
                             continue;
@@ -879,6 +895,7 @@ static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream
     else if (a.out && e5) mx_lastaxis_bf16_kernel<MODE, true, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
     else if (a.out) mx_lastaxis_bf16_kernel<MODE, true, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
     else if (e5) mx_lastaxis_bf16_kernel<MODE, false, CK_E5M2><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
+    else if (MODE != RZ && a.direct >= 2) mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3N><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
     else mx_lastaxis_bf16_kernel<MODE, false, CK_E4M3><<<g, kLastBfThreads, 0, st>>>(a, nvec, lanes, rl);
     return check_launch();
 }
@@ -900,11 +917,13 @@ static int launch_strided_bf16(const MxArgs& a, cudaStream_t st) {
     if (a.transposed) {
         if (a.out) return e5 ? launch_strided_bf16_one<MODE, true, CK_E5M2, true>(a, st)
                              : launch_strided_bf16_one<MODE, true, CK_E4M3, true>(a, st);
+        if (!e5 && MODE != RZ && a.direct >= 2) return launch_strided_bf16_one<MODE, false, CK_E4M3N, true>(a, st);
         return e5 ? launch_strided_bf16_one<MODE, false, CK_E5M2, true>(a, st)
                   : launch_strided_bf16_one<MODE, false, CK_E4M3, true>(a, st);
     }
     if (a.out) return e5 ? launch_strided_bf16_one<MODE, true, CK_E5M2, false>(a, st)
                          : launch_strided_bf16_one<MODE, true, CK_E4M3, false>(a, st);
+    if (!e5 && MODE != RZ && a.direct >= 2) return launch_strided_bf16_one<MODE, false, CK_E4M3N, false>(a, st);
     return e5 ? launch_strided_bf16_one<MODE, false, CK_E5M2, false>(a, st)
               : launch_strided_bf16_one<MODE, false, CK_E4M3, false>(a, st);
 }

@@ -168,10 +168,10 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
                 a.scales[sidx] = (uint8_t)(fb.ok ? fb.E : (uint32_t)scale_exp_from_absmax(bm << 16, a.fmt.emax_elem, a.scale_emax));
             }
             uint32_t cw[2] = {0, 0};
-            if (fb.ok && MODE != RZ && a.direct8) {
+            if (fb.ok && use_direct<false, CK == CK_NONE ? CK_E4M3 : CK, MODE>(a)) {
                 const float cf = direct_factor<MODE>(fb.inv);
-                cw[0] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[0], p[1], cf, cf, cf, cf);
-                cw[1] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[2], p[3], cf, cf, cf, cf);
+                cw[0] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[0], p[1], cf, cf, cf, cf, a.direct);
+                cw[1] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[2], p[3], cf, cf, cf, cf, a.direct);
             } else if (fb.ok) {
                 const uint32_t mp = a.fp_mp_base + fb.E * 0x00800080u;
                 float q[8];
@@ -212,10 +212,13 @@ static int launch_softmax_rows_one(const MxArgs& a, const uint16_t* table, int64
 template <int MODE>
 static int launch_softmax_quantize(const MxArgs& a, const uint16_t* table, int64_t rows, int cols, cudaStream_t st) {
     const bool e5 = a.fmt.ebits == 5;
+    const bool narrow = !e5 && MODE != RZ && a.direct >= 2;           // fp6 / fp4: see CK_E4M3N
     if (a.out) return e5 ? launch_softmax_rows_one<MODE, CK_E5M2, true>(a, table, rows, cols, st)
-                         : launch_softmax_rows_one<MODE, CK_E4M3, true>(a, table, rows, cols, st);
+                         : narrow ? launch_softmax_rows_one<MODE, CK_E4M3N, true>(a, table, rows, cols, st)
+                                  : launch_softmax_rows_one<MODE, CK_E4M3, true>(a, table, rows, cols, st);
     return e5 ? launch_softmax_rows_one<MODE, CK_E5M2, false>(a, table, rows, cols, st)
-              : launch_softmax_rows_one<MODE, CK_E4M3, false>(a, table, rows, cols, st);
+              : narrow ? launch_softmax_rows_one<MODE, CK_E4M3N, false>(a, table, rows, cols, st)
+                       : launch_softmax_rows_one<MODE, CK_E4M3, false>(a, table, rows, cols, st);
 }
 
 // Softmax alone through the same kernel (called by mxq_softmax_bf16 for large inputs).

@@ -39,6 +39,11 @@ from .formats import _get_format_params
 from .specs import apply_mx_specs
 from .vector_ops import fused_bf16_ok
 
+# SMs the token-chunked forward leaves to the collectives that run beside its GEMMs (MXQ_TP_COMM_SMS
+# overrides; 0 = none).  NCCL's reduce-scatter of the fp32 partial sums wants about 32 CTAs: at 4 ranks
+# 16384 tokens took 3.10 ms with no room, 3.03 ms with 32 SMs, 3.12 ms with 16.
+_COMM_SMS = 32
+
 
 def shard_bounds(n, rank, world, multiple=1):
     """[lo, hi) of rank's contiguous shard of n items; n must split evenly into
@@ -284,6 +289,15 @@ class TensorParallelFFN(torch.nn.Module):
         out = quantize_elemwise_op(out, sp, round=sp["round_output"])
         return out.to(h.dtype)
 
+    def _gemm_sms(self, device):
+        """SMs the GEMMs keep while a collective runs beside them: the device's SMs less MXQ_TP_COMM_SMS
+        (0 = all: the GEMM is persistent, one CTA per SM, so without room the collective's CTAs only
+        start when the GEMM ends and nothing overlaps)."""
+        reserve = int(os.environ.get("MXQ_TP_COMM_SMS", str(_COMM_SMS)))
+        if reserve <= 0:
+            return 0
+        return max(torch.cuda.get_device_properties(device).multi_processor_count - reserve, 2)
+
     def _token_chunks(self, local_tokens):
         """Token chunks of the pipelined forward: more than one only with several ranks, for whole
         128-row groups per chunk; MXQ_TP_TOKEN_CHUNKS overrides (1 = off)."""
@@ -323,30 +337,31 @@ class TensorParallelFFN(torch.nn.Module):
 
         nxt = gather(0)
         outs, works = [], []
-        for c in range(n_chunks):
-            xc, xs, ws = nxt
-            for w in ws:
-                w.wait()
-            if c + 1 < n_chunks:
-                nxt = gather(c + 1)
-            M = W * rc
-            gate = be.gemm_mx(xc, xs, pg.codes, pg.scales, 1, M, Il, H, px.container, pg.container, out_dtype=h.dtype,
-                              bfloat_bits=bits, round_mode=out_rnd)[0]
-            up = be.gemm_mx(xc, xs, pu.codes, pu.scales, 1, M, Il, H, px.container, pu.container, out_dtype=h.dtype,
-                            bfloat_bits=bits, round_mode=out_rnd)[0]
-            if fused:
-                ac, as_ = be.swiglu_quantize_mx(gate, up, sp["scale_bits"] or 8, eb, mb, mn, sp["mx_flush_fp32_subnorms"],
-                                                _MODE[rnd])
-                ak = 1 if eb == 5 else 0
-            else:
-                act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
-                pa = _pack(quantize_elemwise_op(act, sp, round=sp["round_output"]), af, sp, rnd, True)
-                ac, as_, ak = pa.codes, pa.scales, pa.container
-            part = be.gemm_mx(ac, as_, pd.codes, pd.scales, 1, M, H, Il, ak, pd.container, out_dtype=torch.float32,
-                              bfloat_bits=0, round_mode=-1)[0]
-            o = torch.empty((rc, H), dtype=torch.float32, device=h.device)
-            works.append(dist.reduce_scatter_tensor(o, part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
-            outs.append(o)
+        with be.gemm_sm_budget(self._gemm_sms(h.device)):      # every GEMM here has an exchange beside it
+            for c in range(n_chunks):
+                xc, xs, ws = nxt
+                for w in ws:
+                    w.wait()
+                if c + 1 < n_chunks:
+                    nxt = gather(c + 1)
+                M = W * rc
+                gate = be.gemm_mx(xc, xs, pg.codes, pg.scales, 1, M, Il, H, px.container, pg.container, out_dtype=h.dtype,
+                                  bfloat_bits=bits, round_mode=out_rnd)[0]
+                up = be.gemm_mx(xc, xs, pu.codes, pu.scales, 1, M, Il, H, px.container, pu.container, out_dtype=h.dtype,
+                                bfloat_bits=bits, round_mode=out_rnd)[0]
+                if fused:
+                    ac, as_ = be.swiglu_quantize_mx(gate, up, sp["scale_bits"] or 8, eb, mb, mn, sp["mx_flush_fp32_subnorms"],
+                                                    _MODE[rnd])
+                    ak = 1 if eb == 5 else 0
+                else:
+                    act = simd_ops.simd_mul(activations.silu(gate, mx_specs=sp), up, mx_specs=sp)
+                    pa = _pack(quantize_elemwise_op(act, sp, round=sp["round_output"]), af, sp, rnd, True)
+                    ac, as_, ak = pa.codes, pa.scales, pa.container
+                part = be.gemm_mx(ac, as_, pd.codes, pd.scales, 1, M, H, Il, ak, pd.container, out_dtype=torch.float32,
+                                  bfloat_bits=0, round_mode=-1)[0]
+                o = torch.empty((rc, H), dtype=torch.float32, device=h.device)
+                works.append(dist.reduce_scatter_tensor(o, part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                outs.append(o)
         for w in works:
             w.wait()
         out = quantize_elemwise_op(torch.cat(outs, dim=0), sp, round=sp["round_output"])

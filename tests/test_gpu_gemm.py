@@ -230,3 +230,26 @@ def test_config3_gemm_full_size_sampled(be):
 def test_config5_gemm_full_size_sampled(be):
     """Config 5 gate/up projection: 16384 tokens x 8192 -> 28672, fp8_e4m3 activations x fp4_e2m1 weights."""
     _sampled_gemm_check(be, 16384, 28672, 8192, "fp8_e4m3", "fp4_e2m1", n_rows=16, n_cols=384, seed=1)
+
+
+def test_gemm_sm_budget_leaves_results_unchanged(be):
+    """A smaller SM budget only changes how many persistent CTAs walk the tiles: the output bits stay, for the
+    CTA-pair engine (4096 x 4096 x 2048) and the single-CTA one (512 x 384 x 256); the setter hands back
+    the previous value and the block form restores it."""
+    for M, N, K in ((4096, 4096, 2048), (512, 384, 256)):
+        g = torch.Generator().manual_seed(M)
+        A = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+        B = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+        _, ca, sa, ka = quant_operand(be, A, "fp8_e4m3", M)
+        _, cb, sb, kb = quant_operand(be, B, "fp8_e4m3", N)
+        run = lambda: be.gemm_mx(ca, sa, cb, sb, 1, M, N, K, ka, kb, torch.bfloat16, 16, 0, None, 0)
+        full = run()
+        assert be.lib().mxq_gemm_sm_budget(-1) == 0
+        for sms in (116, 7, 1):
+            with be.gemm_sm_budget(sms):
+                assert be.lib().mxq_gemm_sm_budget(-1) == sms
+                part = run()
+            assert be.lib().mxq_gemm_sm_budget(-1) == 0
+            assert torch.equal(full, part), (M, N, K, sms)
+    torch.cuda.synchronize()
+    assert be.device_status() == 0

@@ -126,6 +126,27 @@ def test_mx_bf16_ties_at_every_relative_exponent(be, fmt, round):
         assert oracle.same_values(got, np.ascontiguousarray(want[:n].T)), (fmt, round, dt, "axis 0")
 
 
+@pytest.mark.parametrize("fmt", ["fp8_e4m3", "fp8_e5m2", "fp6_e3m2", "fp6_e2m3", "fp4_e2m1"])
+@pytest.mark.parametrize("round", list(ROUNDS))
+def test_mx_codes_only_ties_at_every_relative_exponent(be, fmt, round):
+    """The packing-only kernels (no dequantized output: element rounding by the hardware conversions
+    where the format has one) on the same tie walk, blocks along the last axis and along axis 0 with
+    transposed codes; the packed operand, decoded, must equal the oracle's values bit for bit."""
+    eb, mb, mn = oracle.FORMATS[fmt]
+    x = _anchored_bf16_blocks()
+    want = oracle.quantize_mx(x, fmt, axis=-1, block=32, scale_bits=8, round=round)
+    xb = torch.as_tensor(x).to(torch.bfloat16).cuda()
+    _, codes, scales = be.quantize_mx(xb, 8, eb, mb, mn, 32, 1, False, ROUNDS[round], want_dq=False, want_codes=True)
+    got = dequant_packed(codes.cpu().numpy(), scales.cpu().numpy(), 32, 1, eb, mb)
+    assert oracle.same_values(got, want), (fmt, round, "last axis")
+    n = x.shape[0] // 8 * 8
+    xt = torch.as_tensor(np.ascontiguousarray(x[:n].T)).to(torch.bfloat16).cuda()[None]     # [1, 32, n]
+    _, codes, scales = be.quantize_mx(xt, 8, eb, mb, mn, 32, 1, False, ROUNDS[round], want_dq=False, want_codes=True,
+                                      transposed=True)
+    got = dequant_packed(codes.cpu().numpy()[0], scales.cpu().numpy()[0], 32, 1, eb, mb)   # [n, 32], [n, 1]
+    assert oracle.same_values(got, want[:n]), (fmt, round, "axis 0, transposed codes")
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("axis", [0, 1, 2])
 def test_mx_dtypes_and_axes(be, dtype, axis):
