@@ -542,10 +542,8 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float s0 = __uint_as_float((uint32_t)sig_tab[g[i] & 0xffffu] << 16);
-                const float s1 = __uint_as_float((uint32_t)sig_tab[g[i] >> 16] << 16);
-                const uint32_t y = rb2(bf_lo(g[i]) * s0, bf_hi(g[i]) * s1);          // gate * sigmoid, rounded
-                o[i] = rb2(bf_lo(y) * bf_lo(up[i]), bf_hi(y) * bf_hi(up[i]));        // ... * up, rounded
+                const uint32_t s2 = (uint32_t)sig_tab[g[i] & 0xffffu] | ((uint32_t)sig_tab[g[i] >> 16] << 16);
+                o[i] = mul_bf16x2(mul_bf16x2(g[i], s2), up[i]);    // gate * sigmoid, rounded, then * up, rounded
             }
             raw[u] = make_uint4(o[0], o[1], o[2], o[3]);
         }

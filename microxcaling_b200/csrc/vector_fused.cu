@@ -116,10 +116,10 @@ silu_tab_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ u
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t b0 = tab[g[i] & 0xffffu], b1 = tab[g[i] >> 16];
-            uint32_t y = rb2(bf_lo(g[i]) * __uint_as_float(b0 << 16), bf_hi(g[i]) * __uint_as_float(b1 << 16));
-            if (HAS_UP) y = rb2(bf_lo(y) * bf_lo(u[i]), bf_hi(y) * bf_hi(u[i]));
-            o[i] = y;
             sg[i] = b0 | (b1 << 16);
+            uint32_t y = mul_bf16x2(g[i], sg[i]);                   // gate * sigmoid, rounded
+            if (HAS_UP) y = mul_bf16x2(y, u[i]);                    // ... * up, rounded
+            o[i] = y;
         }
         out[v] = make_uint4(o[0], o[1], o[2], o[3]);
         if (WANT_SIG) sig[v] = make_uint4(sg[0], sg[1], sg[2], sg[3]);
@@ -186,8 +186,7 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
                 const uint32_t q[4] = {kept[k].x, kept[k].y, kept[k].z, kept[k].w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float lo = bf_lo(q[j]), hi = bf_hi(q[j]);
-                    const uint32_t sq = rb2(lo * lo, hi * hi);
+                    const uint32_t sq = mul_bf16x2(q[j], q[j]);
                     acc += bf_lo(sq);
                     acc += bf_hi(sq);
                 }
@@ -199,8 +198,7 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
                 const uint32_t q[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float lo = bf_lo(q[k]), hi = bf_hi(q[k]);
-                    const uint32_t sq = rb2(lo * lo, hi * hi);
+                    const uint32_t sq = mul_bf16x2(q[k], q[k]);
                     acc += bf_lo(sq);
                     acc += bf_hi(sq);
                 }
@@ -229,6 +227,7 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
         }
         __syncthreads();
         const float ri = r_shared;
+        const uint32_t ri2 = (__float_as_uint(ri) >> 16) * 0x10001u;         // (ri, ri) as a packed pair
         uint16_t* orow = out + row * hidden;
         uint16_t* nrow = xnorm ? xnorm + row * hidden : nullptr;
         if (vec) {
@@ -248,9 +247,9 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
                 uint32_t o[4], nn[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint32_t n2 = rb2(bf_lo(q[k]) * ri, bf_hi(q[k]) * ri);
-                    uint32_t y2 = rb2(bf_lo(wq[k]) * bf_lo(n2), bf_hi(wq[k]) * bf_hi(n2));
-                    if (b) y2 = rb2(bf_lo(y2) + bf_lo(bq[k]), bf_hi(y2) + bf_hi(bq[k]));
+                    const uint32_t n2 = mul_bf16x2(q[k], ri2);
+                    uint32_t y2 = mul_bf16x2(wq[k], n2);
+                    if (b) y2 = add_bf16x2(y2, bq[k]);
                     o[k] = y2;
                     nn[k] = n2;
                 }
