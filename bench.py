@@ -665,6 +665,36 @@ def main():
         h2d = 8 * hx.numel() * 2 + hxf.numel() * 4
         d2h = 8 * hx.numel() * 2 + hxf.numel() * 2
 
+        # what the host side allows: the same bytes as plain pinned copies, both directions at once on two
+        # streams, no kernel -- every rank at the same time, so shared host memory and root ports show up
+        def copies_only():
+            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            dx, dxf = torch.empty_like(hx, device=dev), torch.empty_like(hxf, device=dev)
+            dy, hy = torch.empty_like(hx, device=dev), torch.empty_like(hx).pin_memory()
+            assert hxf.numel() == hx.numel()
+
+            def once():
+                with torch.cuda.stream(s_in):
+                    for _ in range(8):
+                        dx.copy_(hx, non_blocking=True)
+                    dxf.copy_(hxf, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    for _ in range(9):
+                        hy.copy_(dy, non_blocking=True)
+                torch.cuda.synchronize()
+            once()
+            barrier()
+            c0 = time.perf_counter()
+            for _ in range(2):
+                once()
+            barrier()
+            return (time.perf_counter() - c0) / 2
+        copy_s = copies_only()
+        if world > 1:
+            t = torch.tensor([copy_s], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            copy_s = float(t.item())
+
         value = world * STEP_BYTES * K / (total_ms * 1e-3) / 1e9
         strided_ms, last_ms = group_ms[0] / 4, group_ms[1] / 4
         achieved = MX_PASS_BYTES / (strided_ms * 1e-3) / 1e9
@@ -684,7 +714,11 @@ def main():
                              "ew_f32_to_bf16_rne_kernel": {"gbs": EW_PASS_BYTES / (group_ms[2] * 1e-3) / 1e9,
                                                                 "frac": EW_PASS_BYTES / (group_ms[2] * 1e-3) / 1e9 / hbm}}},
             "e2e": {"value": world * STEP_BYTES / e2e_s / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3,
+                    "copies_only": {"value": world * STEP_BYTES / copy_s / 1e9, "unit": "GB/s",
+                                    "note": "the same metric with the step's bytes moved as plain pinned copies, "
+                                            "both directions at once, by every rank at the same time: the host-side "
+                                            "ceiling of e2e on this box"}},
             "gpu_launches": PASSES * K,
             "clocks": clocks,
         }

@@ -429,19 +429,38 @@ __device__ __forceinline__ uint32_t code_quad(float q0, float q1, float q2, floa
 // has 8 significant bits, so x / spacing is never within 2^-8 of a half-way point without being on it).
 // c = 2^-s (exact reciprocal of the block scale) or 2^-s * (1 + 2^-12); the products are exact in fp32
 // (8 x 13 significant bits).  The sign travels through the conversion.  Two pairs -> four code bytes.
-template <int CK>
-__device__ __forceinline__ uint32_t direct_pair(float lo, float hi, int kind) {
+// KIND as in MxArgs::direct (1: the container itself, 2 fp6_e3m2, 3 fp6_e2m3, 4 fp4_e2m1)
+template <int CK, int KIND>
+__device__ __forceinline__ uint32_t direct_pair(float lo, float hi) {
     if (CK == CK_E5M2) return encode2_e5m2(lo, hi);
     if (CK != CK_E4M3N) return encode2_e4m3(lo, hi);
-    if (kind == 2) return encode2_via_e3m2(lo, hi);
-    return kind == 3 ? encode2_via_e2m3(lo, hi) : encode2_via_e2m1(lo, hi);
+    return KIND == 2 ? encode2_via_e3m2(lo, hi) : KIND == 3 ? encode2_via_e2m3(lo, hi) : encode2_via_e2m1(lo, hi);
 }
+template <int CK, int KIND>
+__device__ __forceinline__ uint32_t code_quad_direct_k(uint32_t w01, uint32_t w23, float c0, float c1, float c2, float c3) {
+    const float v0 = __uint_as_float(w01 << 16) * c0, v1 = __uint_as_float(w01 & 0xffff0000u) * c1;
+    const float v2 = __uint_as_float(w23 << 16) * c2, v3 = __uint_as_float(w23 & 0xffff0000u) * c3;
+    return __byte_perm(direct_pair<CK, KIND>(v0, v1), direct_pair<CK, KIND>(v2, v3), 0x5410);
+}
+// one decision on the narrow format per call, not per pair (it is warp-uniform but the compiler keeps it a branch)
 template <int CK>
 __device__ __forceinline__ uint32_t code_quad_direct(uint32_t w01, uint32_t w23, float c0, float c1, float c2, float c3,
                                                      int kind) {
-    const float v0 = __uint_as_float(w01 << 16) * c0, v1 = __uint_as_float(w01 & 0xffff0000u) * c1;
-    const float v2 = __uint_as_float(w23 << 16) * c2, v3 = __uint_as_float(w23 & 0xffff0000u) * c3;
-    return __byte_perm(direct_pair<CK>(v0, v1, kind), direct_pair<CK>(v2, v3, kind), 0x5410);
+    if (CK != CK_E4M3N) return code_quad_direct_k<CK, 1>(w01, w23, c0, c1, c2, c3);
+    if (kind == 2) return code_quad_direct_k<CK, 2>(w01, w23, c0, c1, c2, c3);
+    if (kind == 3) return code_quad_direct_k<CK, 3>(w01, w23, c0, c1, c2, c3);
+    return code_quad_direct_k<CK, 4>(w01, w23, c0, c1, c2, c3);
+}
+// eight elements (four packed pairs) scaled by one factor -> eight code bytes
+template <int CK>
+__device__ __forceinline__ uint2 code_oct_direct(const uint32_t* w, float c, int kind) {
+    if (CK != CK_E4M3N)
+        return make_uint2(code_quad_direct_k<CK, 1>(w[0], w[1], c, c, c, c), code_quad_direct_k<CK, 1>(w[2], w[3], c, c, c, c));
+    if (kind == 2)
+        return make_uint2(code_quad_direct_k<CK, 2>(w[0], w[1], c, c, c, c), code_quad_direct_k<CK, 2>(w[2], w[3], c, c, c, c));
+    if (kind == 3)
+        return make_uint2(code_quad_direct_k<CK, 3>(w[0], w[1], c, c, c, c), code_quad_direct_k<CK, 3>(w[2], w[3], c, c, c, c));
+    return make_uint2(code_quad_direct_k<CK, 4>(w[0], w[1], c, c, c, c), code_quad_direct_k<CK, 4>(w[2], w[3], c, c, c, c));
 }
 // whether a kernel built for container CK rounds its elements with the conversions
 template <bool WANT_DQ, int CK, int MODE>
@@ -556,7 +575,12 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
         const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
         uint32_t m2 = amax_bf16x2(amax_bf16x2(amax_bf16x2(w[0] & 0x7fff7fffu, w[1]), w[2]), w[3]);
         uint32_t m = max(m2 & 0xffffu, m2 >> 16);
-        for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+        if (lanes_per_block == 4) {                                  // blocks of 32: the usual case, unrolled
+            m = max(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = max(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        } else {
+            for (int s = 1; s < lanes_per_block; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+        }
         const FastBlock fb = fast_block(m >> 7, a);
         if (CK != CK_NONE && live[u] && (threadIdx.x & (lanes_per_block - 1)) == 0) {
             // 8 blocks further along the row = two 512-byte chunks of the GEMM scale layout
@@ -586,8 +610,7 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
         if (use_direct<WANT_DQ, CK, MODE>(a)) {
             if (live[u]) {
                 const float cf = direct_factor<MODE>(fb.inv);
-                reinterpret_cast<uint2*>(a.codes)[v] = make_uint2(code_quad_direct<CK>(w[0], w[1], cf, cf, cf, cf, a.direct),
-                                                                   code_quad_direct<CK>(w[2], w[3], cf, cf, cf, cf, a.direct));
+                reinterpret_cast<uint2*>(a.codes)[v] = code_oct_direct<CK>(w, cf, a.direct);
             }
             continue;
         }

@@ -100,27 +100,49 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
         const uint32_t mb = __float_as_uint(m) >> 16;
         const uint32_t mm2 = mb | (mb << 16);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t tiny = 0xffffffffu;                                // packed minimum of (e - 1), zeros wrap to the top
+        uint32_t dmax2 = 0;                                         // packed maximum of |d|
+        const char* tabb = reinterpret_cast<const char*>(tab);
 #pragma unroll
         for (int k = 0; k < kSqMaxVec; ++k) {
             if (lane + 32 * k < nchunk) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t d2 = sub_bf16x2(w[k][i], mm2) & 0x7fff7fffu;       // |d|: d <= 0 (NaN stays NaN)
-                    const uint32_t e2 = (uint32_t)tab[d2 & 0xffffu] | ((uint32_t)tab[d2 >> 16] << 16);
+                    dmax2 = vmax_u16x2(dmax2, d2);
+                    const uint32_t off2 = d2 << 1;                  // byte offsets into the table, one per lane
+                    const uint32_t e_lo = *reinterpret_cast<const uint16_t*>(tabb + (off2 & 0xffffu));
+                    const uint32_t e_hi = *reinterpret_cast<const uint16_t*>(tabb + (off2 >> 16));
+                    const uint32_t e2 = __byte_perm(e_lo, e_hi, 0x5410);
                     acc[i] += bf_lo(e2);
                     acc[i] += bf_hi(e2);
-                    tiny = vmin_u16x2(tiny, e2 - 0x00010001u);
                     w[k][i] = e2;
                 }
             }
         }
         float accs = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        uint32_t dmax = max(dmax2 & 0xffffu, dmax2 >> 16);
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) accs += __shfl_xor_sync(0xffffffffu, accs, s);
-        uint32_t tmin = min(tiny & 0xffffu, tiny >> 16);
+        for (int s = 16; s > 0; s >>= 1) {
+            accs += __shfl_xor_sync(0xffffffffu, accs, s);
+            dmax = max(dmax, __shfl_xor_sync(0xffffffffu, dmax, s));
+        }
+        // A nonzero e below 2^-115 (exponent field under 12) can only come from |d| > 79.5 (pattern 0x429f).
+        // Rows with such a |d| (masked scores at -inf among them) are searched for one: packed minimum of
+        // (e - 1), zeros wrap to the top.
+        uint32_t tmin = 0xffffu;
+        if (dmax >= 0x429fu) {
+            uint32_t tiny = 0xffffffffu;
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) tmin = min(tmin, __shfl_xor_sync(0xffffffffu, tmin, s));
+            for (int k = 0; k < kSqMaxVec; ++k) {
+                if (lane + 32 * k < nchunk) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) tiny = vmin_u16x2(tiny, w[k][i] - 0x00010001u);
+                }
+            }
+            tmin = min(tiny & 0xffffu, tiny >> 16);
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) tmin = min(tmin, __shfl_xor_sync(0xffffffffu, tmin, s));
+        }
         const float sum = rb(accs);
         const float rsum = __frcp_rn(sum);
         // e / sum is computed as e * (1 / sum) with 1 / sum correctly rounded: e and sum have 8 significant bits
@@ -156,7 +178,8 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             }
             if (CK == CK_NONE) continue;
             // ---- MX packing of the 8 probabilities this lane holds (block = 4 neighbouring lanes) ----
-            uint32_t b2 = amax_bf16x2(amax_bf16x2(amax_bf16x2(p[0] & 0x7fff7fffu, p[1]), p[2]), p[3]);
+            // probabilities are non-negative (or NaN, whose patterns sort above every number): integer maxima
+            const uint32_t b2 = vmax_u16x2(vmax_u16x2(p[0], p[1]), vmax_u16x2(p[2], p[3])) & 0x7fff7fffu;
             uint32_t bm = max(b2 & 0xffffu, b2 >> 16);
             bm = max(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
             bm = max(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
@@ -170,8 +193,8 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             uint32_t cw[2] = {0, 0};
             if (fb.ok && use_direct<false, CK == CK_NONE ? CK_E4M3 : CK, MODE>(a)) {
                 const float cf = direct_factor<MODE>(fb.inv);
-                cw[0] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[0], p[1], cf, cf, cf, cf, a.direct);
-                cw[1] = code_quad_direct<CK == CK_NONE ? CK_E4M3 : CK>(p[2], p[3], cf, cf, cf, cf, a.direct);
+                const uint2 c8 = code_oct_direct<CK == CK_NONE ? CK_E4M3 : CK>(p, cf, a.direct);
+                cw[0] = c8.x; cw[1] = c8.y;
             } else if (fb.ok) {
                 const uint32_t mp = a.fp_mp_base + fb.E * 0x00800080u;
                 float q[8];
