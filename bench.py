@@ -384,7 +384,10 @@ def mx_ffn_block(torch, dist, dev, rank, world, T):
                           "%s)" % (world, "single GPU, no exchange" if world == 1 else
                                    "down-projection GEMM scatters its fp32 tiles into the owners' buffers over "
                                    "peer memory, then an ordered slab sum" if fused_scatter else
-                                   "NCCL reduce-scatter of fp32 partials"),
+                                   "NCCL reduce-scatter of fp32 partials" +
+                                   ("; %d token chunks, exchanges of a chunk under the GEMMs of its neighbours, "
+                                    "%d SMs left to NCCL" % (ffn._token_chunks(T // world), ffn._comm_sms())
+                                    if ffn._token_chunks(T // world) > 1 else "")),
            "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "scaling": "strong",
            "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "library default")}
     # ---- numerics of the sharded block: 32 tokens per rank against the unsharded block on rank 0 ----

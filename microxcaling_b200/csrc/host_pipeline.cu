@@ -2,7 +2,8 @@
 // memory and put the result back in host memory.  The tensor is cut into
 // chunks of whole blocks; chunk i's host->device copy, kernel and device->host
 // copy run on one of three internal streams, so the copy engines in both
-// directions and the SMs work on different chunks at the same time.  PCIe is
+// directions and the SMs work on different chunks at the same time (chunks are
+// short at both ends of the tensor, where a copy has nothing to overlap).  PCIe is
 // the bound here (two copies of 2-4 bytes per element against a kernel that
 // needs a few percent of that time), so the pipeline's job is to keep both
 // directions of the link busy.
@@ -12,8 +13,14 @@
 
 namespace mxq {
 
-constexpr int kPipeSlots = 3;
-constexpr int64_t kChunkBytes = int64_t(16) << 20;     // default target of input bytes per chunk
+#ifndef MXQ_PIPE_SLOTS
+#define MXQ_PIPE_SLOTS 3
+#endif
+#ifndef MXQ_PIPE_CHUNK_MB
+#define MXQ_PIPE_CHUNK_MB 16
+#endif
+constexpr int kPipeSlots = MXQ_PIPE_SLOTS;
+constexpr int64_t kChunkBytes = int64_t(MXQ_PIPE_CHUNK_MB) << 20;     // target of input bytes per chunk
 
 static constexpr int64_t chunk_bytes() { return kChunkBytes; }
 
@@ -57,11 +64,17 @@ static int run_chunks(const void* h_in, void* h_out, int in_es, int out_es, int6
     if (cudaEventRecord(p->begin, user) != cudaSuccess) return MXQ_ERR_CUDA;
     for (int i = 0; i < kPipeSlots; ++i)
         if (cudaStreamWaitEvent(p->s[i], p->begin, 0) != cudaSuccess) return MXQ_ERR_CUDA;
+    // Chunk sizes ramp up from upc / 8 and down again at the end: the first chunk's host->device copy and the
+    // last chunk's device->host copy are the only transfers nothing overlaps, so they are kept short.
+    const int64_t min_units = std::max<int64_t>(1, upc / 8);
     int64_t done_units = 0;
     for (int64_t c = 0; done_units < units; ++c) {
         const int slot = (int)(c % kPipeSlots);
         cudaStream_t st = p->s[slot];
-        const int64_t n = std::min(upc, units - done_units);
+        const int64_t left = units - done_units;
+        const int64_t up = c < 3 ? std::min(upc, min_units << c) : upc;
+        const int64_t down = std::max(min_units, (left + 1) / 2);
+        const int64_t n = std::min(std::min(up, down), left);
         const int64_t first_elem = done_units * unit_elems;
         const int64_t elems = std::min(n * unit_elems, total_elems - first_elem);
         uint8_t* d_in = reinterpret_cast<uint8_t*>(ws) + slot * slot_bytes;

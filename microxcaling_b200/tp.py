@@ -293,10 +293,14 @@ class TensorParallelFFN(torch.nn.Module):
         """SMs the GEMMs keep while a collective runs beside them: the device's SMs less MXQ_TP_COMM_SMS
         (0 = all: the GEMM is persistent, one CTA per SM, so without room the collective's CTAs only
         start when the GEMM ends and nothing overlaps)."""
-        reserve = int(os.environ.get("MXQ_TP_COMM_SMS", str(_COMM_SMS)))
+        reserve = self._comm_sms()
         if reserve <= 0:
             return 0
         return max(torch.cuda.get_device_properties(device).multi_processor_count - reserve, 2)
+
+    @staticmethod
+    def _comm_sms():
+        return int(os.environ.get("MXQ_TP_COMM_SMS", str(_COMM_SMS)))
 
     def _token_chunks(self, local_tokens):
         """Token chunks of the pipelined forward: more than one only with several ranks, for whole

@@ -306,7 +306,7 @@ def test_config2_full_size_properties(be):
 
 
 @pytest.mark.parametrize("shape,axis", [((1024, 4096), 0), ((1024, 4096), 1), ((3, 700, 96), 1), ((5, 64, 33), 2),
-                                        ((40000,), 0), ((4100, 1000), 0)])
+                                        ((40000,), 0), ((4100, 1000), 0), ((8192, 4096), 0), ((6000, 4096), 1)])
 def test_host_buffer_pipeline(be, shape, axis):
     """mxq_quantize_mx_host / mxq_quantize_elemwise_host (chunked, copies overlapped) == device entry points,
     also through quantize_mx_op on a pinned host tensor with custom_cuda."""
