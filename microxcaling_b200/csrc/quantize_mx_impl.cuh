@@ -569,6 +569,35 @@ __device__ __forceinline__ void lastaxis_bf16_tile_impl(const MxArgs& a, const i
     }
     int64_t sidx0 = 0;
     if (CK != CK_NONE && row_local) sidx0 = scale_index_last(a, (uint32_t)(base >> 2));
+    // Straight-line form of the common packing-only case (whole tile inside the tensor, blocks of 32, one
+    // scale row per warp, elements rounded by the conversion instructions): taken when every block of the
+    // warp's four vectors has a fast-path maximum (one vote), so the hot path has no divergent branch.
+    if (FULL && lanes_per_block == 4 && row_local && use_direct<WANT_DQ, CK, MODE>(a)) {
+        uint32_t mx[kLastBfUnroll];
+        bool ok = true;
+#pragma unroll
+        for (int u = 0; u < kLastBfUnroll; ++u) {
+            const uint32_t m2 = amax_bf16x2(amax_bf16x2(amax_bf16x2(raw[u].x & 0x7fff7fffu, raw[u].y), raw[u].z), raw[u].w);
+            uint32_t m = max(m2 & 0xffffu, m2 >> 16);
+            m = max(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = max(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            mx[u] = m >> 7;
+            ok = ok && ((mx[u] - a.fp_e_lo) <= a.fp_e_span);
+        }
+        if (__all_sync(0xffffffffu, ok)) {
+            const bool lead = (threadIdx.x & 3) == 0;
+            uint2* codes = reinterpret_cast<uint2*>(a.codes) + base;
+#pragma unroll
+            for (int u = 0; u < kLastBfUnroll; ++u) {
+                const uint32_t E = mx[u] - (uint32_t)a.fmt.emax_elem;
+                if (lead) a.scales[sidx0 + u * 1024] = (uint8_t)E;
+                const float cf = direct_factor<MODE>(__uint_as_float((254u << 23) - (E << 23)));
+                const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                codes[u * 32] = code_oct_direct<CK>(w, cf, a.direct);
+            }
+            return;
+        }
+    }
 #pragma unroll
     for (int u = 0; u < kLastBfUnroll; ++u) {
         const int64_t v = base + u * 32;

@@ -183,9 +183,20 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             uint32_t bm = max(b2 & 0xffffu, b2 >> 16);
             bm = max(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
             bm = max(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-            if (c >= nchunk) continue;
             const FastBlock fb = fast_block(bm >> 7, a);
+            // one vote per chunk: when every block of the warp's chunk has a fast-path maximum the packing is
+            // straight-line code (no divergent branch)
+            const bool all_fast = use_direct<false, CK == CK_NONE ? CK_E4M3 : CK, MODE>(a) &&
+                                  __all_sync(0xffffffffu, fb.ok || c >= nchunk);
+            if (c >= nchunk) continue;
             const int blk = c >> 2;
+            if (all_fast) {
+                if ((lane & 3) == 0)
+                    a.scales[a.sf_gemm ? srow + (int64_t)(blk >> 2) * 512 + (blk & 3) : srow + blk] = (uint8_t)fb.E;
+                reinterpret_cast<uint2*>(a.codes + row * cols)[c] =
+                    code_oct_direct<CK == CK_NONE ? CK_E4M3 : CK>(p, direct_factor<MODE>(fb.inv), a.direct);
+                continue;
+            }
             if ((lane & 3) == 0) {
                 const int64_t sidx = a.sf_gemm ? srow + (int64_t)(blk >> 2) * 512 + (blk & 3) : srow + blk;
                 a.scales[sidx] = (uint8_t)(fb.ok ? fb.E : (uint32_t)scale_exp_from_absmax(bm << 16, a.fmt.emax_elem, a.scale_emax));
