@@ -50,7 +50,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // CK == CK_NONE: softmax only (probabilities to a.out); otherwise also (or only, !WANT_P) the MX packing.
-template <int MODE, int CK, bool WANT_P>
+// UNI: the row length is a multiple of 256, so a 16-byte chunk index lane + 32 k is inside the row for all
+// lanes of a warp or for none: the bounds checks are warp-uniform branches (no divergence bookkeeping).
+template <int MODE, int CK, bool WANT_P, bool UNI>
 __global__ void __launch_bounds__(kSqThreads, 1)
 softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const int64_t rows, const int cols) {
     extern __shared__ uint4 sq_smem[];
@@ -63,6 +65,7 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
     uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nchunk = cols >> 3;
+    auto inside = [&](int k, int lane_) { return UNI ? 32 * k < nchunk : lane_ + 32 * k < nchunk; };
     const int64_t warps = (int64_t)gridDim.x * kSqWarps;
     uint4* rowbuf = sq_smem + kSqTabBytes / 16 + warp * (kSqRowBytes / 16);
     const uint32_t rowbuf_s = (uint32_t)__cvta_generic_to_shared(rowbuf);
@@ -71,7 +74,12 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
     int64_t row = (int64_t)blockIdx.x * kSqWarps + warp;
     if (row < rows) {
         const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
-        for (int c = lane; c < nchunk; c += 32) cp_async16(rowbuf_s + c * 16, xr + c);
+        if (UNI) {
+#pragma unroll 1
+            for (int k = 0; k < (nchunk >> 5); ++k) cp_async16(rowbuf_s + (lane + 32 * k) * 16, xr + lane + 32 * k);
+        } else {
+            for (int c = lane; c < nchunk; c += 32) cp_async16(rowbuf_s + c * 16, xr + c);
+        }
     }
     cp_async_commit();
     for (; row < rows; row += warps) {
@@ -82,7 +90,7 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
 #pragma unroll
         for (int k = 0; k < kSqMaxVec; ++k) {
             const int c = lane + 32 * k;
-            if (c < nchunk) {
+            if (inside(k, lane)) {
                 const uint4 v = rowbuf[c];
                 w[k][0] = v.x; w[k][1] = v.y; w[k][2] = v.z; w[k][3] = v.w;
                 m2 = max_nan_bf16x2(max_nan_bf16x2(m2, v.x), max_nan_bf16x2(v.y, max_nan_bf16x2(v.z, v.w)));
@@ -91,7 +99,12 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
         __syncwarp();                                               // every lane has its chunks: the buffer is free
         if (row + warps < rows) {
             const uint4* xn = reinterpret_cast<const uint4*>(x + (row + warps) * cols);
-            for (int c = lane; c < nchunk; c += 32) cp_async16(rowbuf_s + c * 16, xn + c);
+            if (UNI) {
+#pragma unroll 1
+                for (int k = 0; k < (nchunk >> 5); ++k) cp_async16(rowbuf_s + (lane + 32 * k) * 16, xn + lane + 32 * k);
+            } else {
+                for (int c = lane; c < nchunk; c += 32) cp_async16(rowbuf_s + c * 16, xn + c);
+            }
         }
         cp_async_commit();
         float m = sq_nan_max(bf_lo(m2), bf_hi(m2));
@@ -104,7 +117,7 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
         const char* tabb = reinterpret_cast<const char*>(tab);
 #pragma unroll
         for (int k = 0; k < kSqMaxVec; ++k) {
-            if (lane + 32 * k < nchunk) {
+            if (inside(k, lane)) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t d2 = sub_bf16x2(w[k][i], mm2) & 0x7fff7fffu;       // |d|: d <= 0 (NaN stays NaN)
@@ -134,7 +147,7 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             uint32_t tiny = 0xffffffffu;
 #pragma unroll
             for (int k = 0; k < kSqMaxVec; ++k) {
-                if (lane + 32 * k < nchunk) {
+                if (inside(k, lane)) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) tiny = vmin_u16x2(tiny, w[k][i] - 0x00010001u);
                 }
@@ -166,7 +179,7 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             if (32 * k >= nchunk) break;                           // warp-uniform: nothing left in this row
             // all 32 lanes take part in the shuffles below; lanes past the row carry zeros
             uint32_t p[4] = {0, 0, 0, 0};
-            if (c < nchunk) {
+            if (UNI || c < nchunk) {
                 if (!exact_div) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) p[i] = rb2(bf_lo(w[k][i]) * rsum, bf_hi(w[k][i]) * rsum);
@@ -187,8 +200,8 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
             // one vote per chunk: when every block of the warp's chunk has a fast-path maximum the packing is
             // straight-line code (no divergent branch)
             const bool all_fast = use_direct<false, CK == CK_NONE ? CK_E4M3 : CK, MODE>(a) &&
-                                  __all_sync(0xffffffffu, fb.ok || c >= nchunk);
-            if (c >= nchunk) continue;
+                                  __all_sync(0xffffffffu, fb.ok || (!UNI && c >= nchunk));
+            if (!UNI && c >= nchunk) continue;
             const int blk = c >> 2;
             if (all_fast) {
                 if ((lane & 3) == 0)
@@ -231,9 +244,9 @@ softmax_rows_kernel(const MxArgs a, const uint16_t* __restrict__ table, const in
     cp_async_wait_all();
 }
 
-template <int MODE, int CK, bool WANT_P>
-static int launch_softmax_rows_one(const MxArgs& a, const uint16_t* table, int64_t rows, int cols, cudaStream_t st) {
-    auto k = softmax_rows_kernel<MODE, CK, WANT_P>;
+template <int MODE, int CK, bool WANT_P, bool UNI>
+static int launch_softmax_rows_uni(const MxArgs& a, const uint16_t* table, int64_t rows, int cols, cudaStream_t st) {
+    auto k = softmax_rows_kernel<MODE, CK, WANT_P, UNI>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSqSmemBytes) != cudaSuccess) {
         cudaGetLastError();
         return MXQ_ERR_CUDA;
@@ -241,6 +254,12 @@ static int launch_softmax_rows_one(const MxArgs& a, const uint16_t* table, int64
     const int64_t ctas = (rows + kSqWarps - 1) / kSqWarps;
     k<<<(unsigned)std::min<int64_t>(ctas, sm_count()), kSqThreads, kSqSmemBytes, st>>>(a, table, rows, cols);
     return check_launch();
+}
+
+template <int MODE, int CK, bool WANT_P>
+static int launch_softmax_rows_one(const MxArgs& a, const uint16_t* table, int64_t rows, int cols, cudaStream_t st) {
+    return cols % 256 == 0 ? launch_softmax_rows_uni<MODE, CK, WANT_P, true>(a, table, rows, cols, st)
+                           : launch_softmax_rows_uni<MODE, CK, WANT_P, false>(a, table, rows, cols, st);
 }
 
 template <int MODE>
