@@ -353,6 +353,24 @@ int mxq_linear_bwd(const void* grad_out, const void* x, const void* w, int dtype
                    void* stream);
 
 /*
+ * One batched MX product as one call (no single reference counterpart: MatMulFunction.forward,
+ * mx/matmul.py:68-86, and BMMFunction.forward, mx/bmm.py:40-59, each make two quantize_mx_op calls
+ * and one torch.matmul / torch.bmm): C[i] = op(A[i]) op(B[i]) for i < batch, both operands MX-quantized
+ * in blocks of 32 along the contraction axis, fp32 accumulation, the output rounded as mxq_gemm_mx
+ * rounds it.  A: [batch, M, K], or [batch, K, M] with a_trans; B: [batch, K, N], or [batch, N, K]
+ * with b_trans.  If a_codes is not NULL, A is already packed (codes [batch, M, K] and scales in the
+ * GEMM layout, e.g. from mxq_softmax_quantize_mx) and `a` is not read.  K % 32 == 0; a transposed
+ * operand needs its row length (M or N) % 4 == 0.  The packed operands live in `workspace`
+ * (256-byte aligned, >= mxq_matmul_workspace_bytes(batch, M, K, N)); nothing is allocated.
+ */
+int64_t mxq_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t K, int64_t N);
+int mxq_matmul_fwd(const void* a, const void* b, int dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                   int a_trans, int b_trans, const mxq_elem_format* a_fmt, const mxq_elem_format* b_fmt,
+                   int scale_bits, int flush_fp32_subnorms, const void* a_codes, const void* a_scales,
+                   void* c, int c_dtype, int out_bfloat_bits, int out_round, const void* bias,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * mxq_linear_fwd for callers that cannot allocate and have no buffer to lend.
  * No counterpart in the reference (which allocates a fresh tensor in every
  * call, mx/cpp/mx.cu:27-28).  Same arguments and result as mxq_linear_fwd

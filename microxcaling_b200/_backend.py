@@ -74,6 +74,11 @@ def lib():
         L.mxq_linear_fwd_train.argtypes = [vp, vp, i32, i64, i64, i64, fp, fp, i32, i32, vp, i32, i32, i32, vp, vp, i64, vp]
         L.mxq_linear_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, fp, fp, fp, fp, i32, i32, vp, vp, i32, i32, i32, i32,
                                      vp, i64, vp]
+        L.mxq_matmul_workspace_bytes.argtypes = [i64, i64, i64, i64]
+        L.mxq_matmul_workspace_bytes.restype = i64
+        L.mxq_matmul_fwd.argtypes = [vp, vp, i32, i64, i64, i64, i64, i32, i32, fp, fp, i32, i32, vp, vp, vp, i32, i32, i32,
+                                     vp, vp, i64, vp]
+        L.mxq_gemm_sm_budget.argtypes = [i32]
         L.mxq_cpu_quantize_mx.argtypes = [vp, vp, i32, i64, i64, i64, i32, i32, i32, i32, f32, i32, i32, vp, i32]
         L.mxq_cpu_quantize_elemwise.argtypes = [vp, vp, i32, i32, i64, i32, i32, f32, i32, i32, i32, vp, i32]
         _lib = L
@@ -418,6 +423,24 @@ def linear_fwd_train(x, w, a_fmt, w_fmt, scale_bits, flush, out_dtype, bfloat_bi
                                      int(scale_bits), int(bool(flush)), _ptr(y), _DT[y.dtype], int(bfloat_bits),
                                      int(out_round), _ptr(bias), _ptr(ws), ws.numel(), _stream(x)))
     return y
+
+
+def matmul_fwd(a, b, batch, M, K, N, a_trans, b_trans, a_fmt, b_fmt, scale_bits, flush, out_dtype, bfloat_bits,
+               out_round, bias=None, a_packed=None):
+    """C [batch, M, N] = op(a) op(b) with both operands MX-quantized in the call; see mxq_matmul_fwd.
+    a_packed: (codes, scales) of an already packed left operand (a is then only a shape donor)."""
+    L = lib()
+    ws = torch.empty(L.mxq_matmul_workspace_bytes(batch, M, K, N), dtype=torch.uint8, device=b.device)
+    c = torch.empty((batch, M, N), dtype=out_dtype, device=b.device)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    ac, as_ = a_packed if a_packed is not None else (None, None)
+    with _device_of(b.device):
+        check(L.mxq_matmul_fwd(None if a_packed is not None else _ptr(a), _ptr(b), _DT[b.dtype], batch, M, K, N,
+                               int(bool(a_trans)), int(bool(b_trans)), ctypes.byref(a_fmt), ctypes.byref(b_fmt),
+                               int(scale_bits), int(bool(flush)), _ptr(ac), _ptr(as_), _ptr(c), _DT[c.dtype],
+                               int(bfloat_bits), int(out_round), _ptr(bias), _ptr(ws), ws.numel(), _stream(b)))
+    return c
 
 
 def linear_bwd(go, x, w, go_fmt_gw, x_fmt_gw, go_fmt_gi, w_fmt_gi, scale_bits, flush, out_dtype, bfloat_bits,

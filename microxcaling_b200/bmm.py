@@ -3,6 +3,7 @@
 use the activation element format."""
 import torch
 
+from ._autograd import call
 from ._mxgemm import mx_gemm
 from .elemwise_ops import quantize_elemwise_op
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
@@ -43,4 +44,4 @@ def bmm(in1, in2, mx_specs=None, name=None):
     if mx_specs is None:
         return torch_bmm(in1, in2)
     mx_specs = apply_mx_specs(mx_specs)
-    return BMMFunction.apply(in1, in2, mx_specs, name)
+    return call(BMMFunction, in1, in2, mx_specs, name)

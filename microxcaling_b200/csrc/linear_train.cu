@@ -134,3 +134,71 @@ extern "C" int mxq_linear_bwd(const void* grad_out, const void* x, const void* w
     }
     return MXQ_OK;
 }
+
+// ---------------------------------------------------------------------------
+// One batched MX product as one call: C[b] = op(A[b]) op(B[b]), both operands MX-quantized along the
+// contraction axis in the call (mx/matmul.py:68-86, mx/bmm.py:40-59).  A is [batch, M, K] or, with
+// a_trans, [batch, K, M]; B is [batch, K, N] or, with b_trans, [batch, N, K].  A may arrive already
+// packed (a_codes / a_scales in the GEMM layout, e.g. probabilities packed by mxq_softmax_quantize_mx);
+// `a` is then not read.
+// ---------------------------------------------------------------------------
+namespace mxq {
+static int pack_batched(uint8_t* codes, uint8_t* scales, int64_t scale_bytes, const void* x, int dtype, int64_t batch,
+                        int64_t rows, int64_t K, bool contraction_last, const mxq_elem_format* f, int scale_bits,
+                        int flush, cudaStream_t st) {
+    if (((rows % 128) != 0 || (K % 128) != 0) && cudaMemsetAsync(scales, 0, (size_t)scale_bytes, st) != cudaSuccess)
+        return MXQ_ERR_CUDA;
+    if (contraction_last)
+        return mxq_quantize_mx(x, nullptr, codes, scales, dtype, batch * rows, K, 1, 32, scale_bits, f->ebits, f->mbits,
+                               f->max_norm, flush, f->round, nullptr, MXQ_SCALES_GEMM_LAYOUT, rows, st);
+    return mxq_quantize_mx(x, nullptr, codes, scales, dtype, batch, K, rows, 32, scale_bits, f->ebits, f->mbits,
+                           f->max_norm, flush, f->round, nullptr, MXQ_SCALES_GEMM_LAYOUT | MXQ_CODES_TRANSPOSED, 0, st);
+}
+}  // namespace mxq
+
+extern "C" int64_t mxq_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t K, int64_t N) {
+    if (batch < 0 || M < 0 || K < 0 || N < 0) return -1;
+    using namespace mxq;
+    return 256 + up256(batch * M * K) + up256(mxq_sf_bytes(batch, M, K)) + up256(batch * N * K) +
+           up256(mxq_sf_bytes(batch, N, K));
+}
+
+extern "C" int mxq_matmul_fwd(const void* a, const void* b, int dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                              int a_trans, int b_trans, const mxq_elem_format* a_fmt, const mxq_elem_format* b_fmt,
+                              int scale_bits, int flush_fp32_subnorms, const void* a_codes, const void* a_scales,
+                              void* c, int c_dtype, int out_bfloat_bits, int out_round, const void* bias,
+                              void* workspace, int64_t workspace_bytes, void* stream) {
+    using namespace mxq;
+    if (batch < 0 || M < 0 || K < 0 || N < 0) return MXQ_ERR_BAD_ARG;
+    if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
+    const bool a_packed = a_codes != nullptr;
+    if ((!a && !a_packed) || (a_packed && !a_scales) || !b || !c || !workspace || !fmt_ok(a_fmt) || !fmt_ok(b_fmt))
+        return MXQ_ERR_BAD_ARG;
+    if (K == 0 || K % 32 != 0) return MXQ_ERR_UNSUPPORTED;
+    // the strided packing kernels of a transposed operand want 8-byte aligned rows
+    if ((a_trans && !a_packed && M % 4 != 0) || (!b_trans && N % 4 != 0)) return MXQ_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return MXQ_ERR_ALIGN;
+    if (workspace_bytes < mxq_matmul_workspace_bytes(batch, M, K, N)) return MXQ_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* p = reinterpret_cast<uint8_t*>(workspace);
+    int* status = reinterpret_cast<int*>(p);
+    p += 256;
+    if (cudaMemsetAsync(status, 0, 256, st) != cudaSuccess) return MXQ_ERR_CUDA;
+    uint8_t* ac = p;            p += up256(batch * M * K);
+    const int64_t a_sf = mxq_sf_bytes(batch, M, K);
+    uint8_t* as = p;            p += up256(a_sf);
+    uint8_t* bc = p;            p += up256(batch * N * K);
+    const int64_t b_sf = mxq_sf_bytes(batch, N, K);
+    uint8_t* bs = p;
+    int rc;
+    if (!a_packed) {
+        rc = pack_batched(ac, as, a_sf, a, dtype, batch, M, K, !a_trans, a_fmt, scale_bits, flush_fp32_subnorms, st);
+        if (rc) return rc;
+    }
+    rc = pack_batched(bc, bs, b_sf, b, dtype, batch, N, K, b_trans != 0, b_fmt, scale_bits, flush_fp32_subnorms, st);
+    if (rc) return rc;
+    return gemm_mx_with_status(a_packed ? a_codes : ac, a_packed ? a_scales : as, bc, bs, c, batch, M, N, K,
+                               a_fmt->ebits == 5 ? 1 : 0, b_fmt->ebits == 5 ? 1 : 0, c_dtype, out_bfloat_bits, out_round,
+                               bias, 0, status, stream);
+}
+

@@ -704,10 +704,12 @@ constexpr int kStrBfThreads = 128;
 // chunk(c, j) = (4c + j) ^ ((c >> 2) & 7), which keeps both the per-column
 // writes and the row-major readout free of bank conflicts.  In the GEMM scale
 // layout the four scale bytes of a column are one 32-bit word.
-template <int MODE, bool WANT_DQ, int CK, bool TRANSPOSED>
+// BPT: consecutive blocks a thread walks in the transposed form: 4, or 1 for tensors so small that four would
+// leave most SMs without a CTA (the operands of an attention head).
+template <int MODE, bool WANT_DQ, int CK, bool TRANSPOSED, int BPT = 4>
 __global__ void __launch_bounds__(kStrBfThreads, (CK == CK_NONE && !TRANSPOSED) ? 6 : 4)
 mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nbgrp) {
-    constexpr int kBlocksPerThread = TRANSPOSED ? 4 : 1;
+    constexpr int kBlocksPerThread = TRANSPOSED ? BPT : 1;
     __shared__ uint4 stage[TRANSPOSED ? kStrBfThreads * 4 * 4 : 1];
     // Columns are numbered across the leading axis: g = p * post + col.  A CTA owns 512 consecutive such
     // columns (four per thread; post % 4 == 0 keeps a thread's four inside one p), so tensors whose `post` is
@@ -838,7 +840,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
                 }
             }
         }
-        if (CK != CK_NONE && TRANSPOSED && ((bb & 1) || b + 1 >= a.nblk)) {
+        if (CK != CK_NONE && TRANSPOSED && ((bb & 1) || bb + 1 >= kBlocksPerThread || b + 1 >= a.nblk)) {
             // write out the staged pair of blocks: 4 lanes per output row
             __syncthreads();
             const int nchunk = ((bb & 1) + 1) * 2;
@@ -860,7 +862,7 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             uint8_t* dst = a.scales + scale_index(a, p, b0, col + i);
-            if (nb == 4) *reinterpret_cast<uint32_t*>(dst) = sf_word[i];
+            if (kBlocksPerThread == 4 && nb == 4) *reinterpret_cast<uint32_t*>(dst) = sf_word[i];
             else for (int k = 0; k < nb; ++k) dst[k] = (uint8_t)(sf_word[i] >> (8 * k));
         }
     }
@@ -953,6 +955,11 @@ static int launch_last_bf16(const MxArgs& a, int64_t nvec, int lanes, cudaStream
 template <int MODE, bool WANT_DQ, int CK, bool TR>
 static int launch_strided_bf16_one(const MxArgs& a, cudaStream_t st) {
     const int64_t col_tiles = (a.pre * a.post + (int64_t)kStrBfThreads * 4 - 1) / ((int64_t)kStrBfThreads * 4);
+    if (TR && !WANT_DQ && col_tiles * ((a.nblk + 3) / 4) < 2 * (int64_t)sm_count()) {
+        // a small operand: one block per thread, four times the CTAs
+        mx_strided_bf16_kernel<MODE, WANT_DQ, CK, TR, 1><<<(unsigned)(col_tiles * a.nblk), kStrBfThreads, 0, st>>>(a, col_tiles, a.nblk);
+        return check_launch();
+    }
     const int64_t nbgrp = TR ? (a.nblk + 3) / 4 : a.nblk;
     const int64_t grid = col_tiles * nbgrp;
     if (grid > 0x7fffffffLL) return MXQ_ERR_TOO_LARGE;

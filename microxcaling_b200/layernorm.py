@@ -2,6 +2,7 @@
 itself is outside the scope of this package."""
 import torch
 
+from ._autograd import call
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
 from .vector_ops import (fused_bf16_ok, vec_add, vec_mul, vec_quantize, vec_recip, vec_reduce_mean, vec_reduce_sum,
                          vec_sqrt, vec_sub)
@@ -62,4 +63,4 @@ class RMSNorm(torch.nn.LayerNorm):
         self.name += postfix
 
     def forward(self, x):
-        return RMSNormFunction.apply(x, self.weight, self.bias, self.eps, self.mx_specs, self.name)
+        return call(RMSNormFunction, x, self.weight, self.bias, self.eps, self.mx_specs, self.name)

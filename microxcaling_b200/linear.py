@@ -10,6 +10,7 @@ tensor-core GEMM with the output rounding fused, where the formats allow it).
 import torch
 import torch.nn.functional as F
 
+from ._autograd import call
 from ._mxgemm import mx_gemm
 from .elemwise_ops import quantize_elemwise_op
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
@@ -162,7 +163,7 @@ def linear(input, weight, bias=None, mx_specs=None, prequantized_weights=False, 
     if mx_specs is None:
         return f_linear(input, weight, bias=bias)
     mx_specs = apply_mx_specs(mx_specs)
-    return LinearFunction.apply(input, weight, bias, mx_specs, prequantized_weights, name, packed_weight)
+    return call(LinearFunction, input, weight, bias, mx_specs, prequantized_weights, name, packed_weight)
 
 
 class Linear(torch.nn.Linear):

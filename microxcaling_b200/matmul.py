@@ -4,6 +4,7 @@ matmul :206-217).  in1 [..., M, K] @ in2 [..., K, N] (or a shared [K, N]), with
 import numpy as np
 import torch
 
+from ._autograd import call
 from ._mxgemm import mx_gemm
 from .elemwise_ops import quantize_elemwise_op
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
@@ -74,4 +75,4 @@ def matmul(in1, in2, bias=None, mx_specs=None, name=None, mode_config="aa"):
     if mx_specs is None:
         return torch_matmul(in1, in2) if bias is None else torch_addmm(bias, in1, in2)
     mx_specs = apply_mx_specs(mx_specs)
-    return MatMulFunction.apply(in1, in2, bias, mx_specs, name, mode_config)
+    return call(MatMulFunction, in1, in2, bias, mx_specs, name, mode_config)

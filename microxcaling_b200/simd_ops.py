@@ -3,6 +3,7 @@
 four binary operators are provided here."""
 import torch
 
+from ._autograd import call
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
 from .vector_ops import vec_add, vec_div, vec_mul, vec_quantize, vec_sub
 
@@ -130,7 +131,7 @@ def _wrap(fn_cls, torch_fn):
         mx_assert_test(mx_specs)
         if mx_specs is None:
             return torch_fn(in1, in2)
-        return fn_cls.apply(in1, in2, apply_mx_specs(mx_specs))
+        return call(fn_cls, in1, in2, apply_mx_specs(mx_specs))
     return f
 
 

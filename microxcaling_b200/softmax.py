@@ -3,6 +3,7 @@ max-subtract, exp (or exp2), sum and divide is rounded to the vector format."""
 import torch
 import torch.nn.functional as F
 
+from ._autograd import call
 from .specs import apply_mx_specs, get_backwards_mx_specs, mx_assert_test
 from .vector_ops import fused_bf16_ok, vec_div, vec_exp, vec_exp2, vec_mul, vec_quantize, vec_reduce_sum, vec_sub
 
@@ -88,7 +89,7 @@ _PENDING = []
 
 def _apply(input, dim, mx_specs, name):
     del _PENDING[:]
-    out = SoftmaxFunction.apply(input, dim, mx_specs, name)
+    out = call(SoftmaxFunction, input, dim, mx_specs, name)
     if _PENDING:
         from .packed import attach_packed
         made, (packed, fmt, rnd), sp = _PENDING.pop()

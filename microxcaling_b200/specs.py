@@ -70,15 +70,43 @@ _QUANT_KEYS = ("w_elem_format", "a_elem_format", "w_elem_format_bp", "a_elem_for
 
 
 class MxSpecs(collections.UserDict):
-    """Dictionary of quantization parameters; unknown keys are rejected."""
+    """Dictionary of quantization parameters; unknown keys are rejected.  Every change bumps `_version`,
+    which lets apply_mx_specs / get_backwards_mx_specs reuse what they derived from an unchanged object
+    (the layers call them on every forward)."""
 
     def __init__(self, *args, **kwargs):
+        self._version = 0
+        self._derived = {}
         super().__init__(*args, **kwargs)
         self.help_strings = dict(_HELP)
         for k, d in _DEFAULTS.items():
             self.data.setdefault(k, d)
         for k in self.data:
             assert k in _DEFAULTS, k
+
+    def __setitem__(self, key, value):
+        self._version += 1
+        self.data[key] = value
+
+    def __delitem__(self, key):
+        self._version += 1
+        del self.data[key]
+
+    def copy(self):
+        c = MxSpecs.__new__(MxSpecs)
+        c._version, c._derived = 0, {}
+        c.data = dict(self.data)
+        c.help_strings = self.help_strings
+        return c
+
+    def _cached(self, what, make):
+        """make() derived from this object, remembered while neither this object nor the result changes."""
+        hit = self._derived.get(what)
+        if hit is not None and hit[0] == self._version and hit[2] == hit[1]._version:
+            return hit[1]
+        out = make()
+        self._derived[what] = (self._version, out, out._version)
+        return out
 
     def safe_json(self, indent=None):
         return json.dumps(self.data, indent=indent,
@@ -96,6 +124,12 @@ def get_default_mx_specs():
 def get_backwards_mx_specs(specs):
     """Copy of `specs` for the backward pass: all quantization off when
     quantize_backprop is False."""
+    if isinstance(specs, MxSpecs):
+        return specs._cached("backward", lambda: _backwards(specs))
+    return _backwards(specs)
+
+
+def _backwards(specs):
     b = specs.copy()
     if b["quantize_backprop"] == False:  # noqa: E712 (0 counts as False, as in the reference)
         for k in _QUANT_KEYS:
@@ -106,10 +140,16 @@ def get_backwards_mx_specs(specs):
 
 def apply_mx_specs(mx_specs, default_mx_specs=None):
     """Overlay the non-None entries of mx_specs on the defaults -> MxSpecs."""
+    if not default_mx_specs and isinstance(mx_specs, MxSpecs):
+        return mx_specs._cached("applied", lambda: _overlay(mx_specs, get_default_mx_specs()))
     if not default_mx_specs:
         default_mx_specs = get_default_mx_specs()
     if not mx_specs:
         return default_mx_specs
+    return _overlay(mx_specs, default_mx_specs)
+
+
+def _overlay(mx_specs, default_mx_specs):
     for k in mx_specs:
         if mx_specs[k] != None:  # noqa: E711
             if k not in default_mx_specs:

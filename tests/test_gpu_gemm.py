@@ -253,3 +253,40 @@ def test_gemm_sm_budget_leaves_results_unchanged(be):
             assert torch.equal(full, part), (M, N, K, sms)
     torch.cuda.synchronize()
     assert be.device_status() == 0
+
+
+@pytest.mark.parametrize("batch,M,K,N", [(1, 256, 128, 256), (3, 200, 96, 136), (2, 384, 256, 64), (4, 128, 2048, 128)])
+@pytest.mark.parametrize("a_trans,b_trans", [(False, False), (False, True), (True, False), (True, True)])
+def test_matmul_fwd_equals_the_three_calls(be, batch, M, K, N, a_trans, b_trans):
+    """mxq_matmul_fwd (both packings and the GEMM chained inside the library) gives the bits of
+    mxq_quantize_mx x 2 + mxq_gemm_mx, for every operand layout, ragged row counts, and with the left
+    operand handed over already packed."""
+    from microxcaling_b200._mxgemm import _cfmt
+    from microxcaling_b200.formats import ElemFormat
+    g = torch.Generator().manual_seed(batch * 1000 + M + N)
+    a = (torch.randn((batch, K, M) if a_trans else (batch, M, K), generator=g) * 2).to(torch.bfloat16).cuda()
+    b = torch.randn((batch, N, K) if b_trans else (batch, K, N), generator=g).to(torch.bfloat16).cuda()
+    fa, fb = ElemFormat.fp6_e3m2, ElemFormat.fp8_e5m2
+    ea, ma, na = oracle.FORMATS["fp6_e3m2"]
+    eb, mb, nb = oracle.FORMATS["fp8_e5m2"]
+    if a_trans:
+        _, ca, sa = be.quantize_mx(a, 8, ea, ma, na, 32, 1, want_dq=False, want_codes=True, transposed=True, gemm_layout=True)
+    else:
+        _, ca, sa = be.quantize_mx(a.reshape(-1, K), 8, ea, ma, na, 32, 1, want_dq=False, want_codes=True,
+                                   gemm_layout=True, rows_per_batch=M)
+    if b_trans:
+        _, cb, sb = be.quantize_mx(b.reshape(-1, K), 8, eb, mb, nb, 32, 1, False, 2, want_dq=False, want_codes=True,
+                                   gemm_layout=True, rows_per_batch=N)
+    else:
+        _, cb, sb = be.quantize_mx(b, 8, eb, mb, nb, 32, 1, False, 2, want_dq=False, want_codes=True, transposed=True,
+                                   gemm_layout=True)
+    bias = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16).float().cuda()
+    want = be.gemm_mx(ca, sa, cb, sb, batch, M, N, K, 0, 1, torch.bfloat16, 16, 0, bias, 0)
+    got = be.matmul_fwd(a, b, batch, M, K, N, a_trans, b_trans, _cfmt(fa, "nearest"), _cfmt(fb, "even"), 8, False,
+                        torch.bfloat16, 16, 0, bias=bias)
+    assert torch.equal(got, want)
+    got2 = be.matmul_fwd(None, b, batch, M, K, N, False, b_trans, _cfmt(fa, "nearest"), _cfmt(fb, "even"), 8, False,
+                         torch.bfloat16, 16, 0, bias=bias, a_packed=(ca, sa))
+    assert torch.equal(got2, want)
+    torch.cuda.synchronize()
+    assert be.device_status() == 0
