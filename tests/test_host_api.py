@@ -238,3 +238,49 @@ def test_shared_exp_method_none_and_block_helpers():
     assert tuple(e.shape) == (6, 2, 1)
     assert torch.equal(e[:, 0, 0], torch.floor(torch.log2(x[:, :32].abs().max(dim=1).values)))
     assert float(_shared_exponents(torch.zeros(4), "max", [0])) == -126.0
+
+
+def test_derived_specs_are_reused_only_while_unchanged():
+    """apply_mx_specs / get_backwards_mx_specs (mx/specs.py:212-276, 193-209) run on every layer call;
+    what they derive from an MxSpecs object is reused until that object, or the derived one, changes."""
+    from microxcaling_b200.specs import MxSpecs, apply_mx_specs, finalize_mx_specs, get_backwards_mx_specs
+    sp = finalize_mx_specs({"a_elem_format": "fp6_e3m2", "w_elem_format": "fp4_e2m1", "block_size": 32, "bfloat": 16})
+    a = apply_mx_specs(sp)
+    assert a is apply_mx_specs(sp) and dict(a) == dict(sp)
+    assert get_backwards_mx_specs(a) is get_backwards_mx_specs(a)
+    sp["round"] = "even"                                     # the source changed: derived again
+    b = apply_mx_specs(sp)
+    assert b is not a and b["round"] == "even" and a["round"] == "nearest"
+    b["bfloat"] = 12                                         # a caller changed the derived object: not handed out again
+    c = apply_mx_specs(sp)
+    assert c is not b and c["bfloat"] == 16
+    off = c.copy()
+    off["quantize_backprop"] = False
+    bw = get_backwards_mx_specs(off)
+    assert bw["a_elem_format"] is None and bw["block_size"] == 0 and off["a_elem_format"] == "fp6_e3m2"
+    assert isinstance(off, MxSpecs) and len(off) == len(sp)
+    assert apply_mx_specs({"bfloat": 16})["bfloat"] == 16    # plain dicts still work
+    with pytest.raises(KeyError):
+        apply_mx_specs({"no_such_key": 1})
+
+
+def test_forward_without_autograd_equals_function_apply():
+    """Layers called where nothing can need a gradient run their forward directly; values are those of
+    Function.apply, and a parameter that requires a gradient still gets one."""
+    import microxcaling_b200 as mx
+    from microxcaling_b200.specs import finalize_mx_specs
+    sp = finalize_mx_specs({"a_elem_format": "fp8_e4m3", "w_elem_format": "fp8_e4m3", "block_size": 32, "bfloat": 16})
+    torch.manual_seed(3)
+    x, w = torch.randn(16, 64), torch.randn(24, 64)
+    with torch.no_grad():
+        y0 = mx.linear(x, w, mx_specs=sp)
+    y1 = mx.linear(x, w, mx_specs=sp)                        # grad mode on, nothing requires grad
+    wg = w.clone().requires_grad_()
+    y2 = mx.linear(x, wg, mx_specs=sp)
+    assert not y0.requires_grad and not y1.requires_grad and y2.requires_grad
+    assert torch.equal(y0, y1) and torch.equal(y0, y2.detach())
+    y2.sum().backward()
+    assert wg.grad is not None and wg.grad.shape == w.shape
+    a, b = torch.randn(2, 8, 64), torch.randn(2, 64, 8)
+    with torch.no_grad():
+        assert torch.equal(mx.bmm(a, b, mx_specs=sp), mx.bmm(a, b.clone().requires_grad_(), mx_specs=sp))
