@@ -1,21 +1,24 @@
 """Process-wide injection of the MX operators into the torch namespaces
-(reference: mx/mx_mapping.py:26-122).  Every mapped function and module takes
-`mx_specs`; the injected wrappers supply it.  Only the operators this package
-implements are mapped: linear / matmul / mm / addmm / bmm, the convolutions,
-the LSTM, softmax, silu, sigmoid, tanh and the four arithmetic functions; the
-reference's normalisation, pooling and remaining activation layers keep their
-stock torch implementations."""
+(reference: mx/mx_mapping.py:26-122), with the reference's full function and
+module tables.  Every mapped function and module takes `mx_specs`; the injected
+wrappers supply it."""
 from contextlib import contextmanager
 
 import torch
 
-from .activations import SiLU, sigmoid, silu, tanh
+from .activations import (GELU, LeakyReLU, ReLU, ReLU6, Sigmoid, SiLU, Tanh, gelu, leaky_relu, relu, relu6, sigmoid, silu,
+                          tanh)
+from .adaptive_avg_pooling import AdaptiveAvgPool2d, adaptive_avg_pool2d
+from .batchnorm import BatchNorm1d, BatchNorm2d, BatchNorm3d, batch_norm
 from .bmm import bmm
 from .convolution import Conv1d, Conv2d, Conv3d, ConvTranspose2d, conv1d, conv2d, conv3d
+from .groupnorm import GroupNorm, group_norm
+from .layernorm import LayerNorm, layer_norm
 from .linear import Linear, linear
 from .matmul import MatMulFunction, matmul
 from .rnn import LSTM
-from .simd_ops import simd_add, simd_div, simd_mul, simd_sub
+from .simd_ops import (simd_add, simd_div, simd_exp, simd_log, simd_mul, simd_norm, simd_reduce_mean, simd_reduce_sum,
+                       simd_square, simd_sub)
 from .softmax import Softmax, softmax
 from .specs import apply_mx_specs
 
@@ -39,13 +42,21 @@ def addmm_mx(bias, in1, in2, mx_specs=None, name=None):
     return MatMulFunction.apply(in1, in2, bias, apply_mx_specs(mx_specs), name)
 
 
-MODULE_MAPPING = {"Linear": Linear, "SiLU": SiLU, "Softmax": Softmax, "Conv1d": Conv1d, "Conv2d": Conv2d,
-                  "Conv3d": Conv3d, "ConvTranspose2d": ConvTranspose2d, "LSTM": LSTM}
+MODULE_MAPPING = {
+    "AdaptiveAvgPool2d": AdaptiveAvgPool2d, "BatchNorm1d": BatchNorm1d, "BatchNorm2d": BatchNorm2d,
+    "BatchNorm3d": BatchNorm3d, "Conv1d": Conv1d, "Conv2d": Conv2d, "Conv3d": Conv3d,
+    "ConvTranspose2d": ConvTranspose2d, "GELU": GELU, "GroupNorm": GroupNorm, "LSTM": LSTM, "LayerNorm": LayerNorm,
+    "LeakyReLU": LeakyReLU, "Linear": Linear, "ReLU": ReLU, "ReLU6": ReLU6, "SiLU": SiLU, "Sigmoid": Sigmoid,
+    "Softmax": Softmax, "Tanh": Tanh,
+}
 FUNCTION_MAPPING = {
-    "linear": linear, "matmul": matmul, "mm": matmul, "addmm": addmm_mx, "bmm": bmm,
-    "conv1d": conv1d, "conv2d": conv2d, "conv3d": conv3d,
-    "softmax": softmax, "silu": silu, "sigmoid": sigmoid, "tanh": tanh,
-    "add": simd_add, "sub": simd_sub, "mul": simd_mul, "div": simd_div,
+    "adaptive_avg_pool2d": adaptive_avg_pool2d, "batch_norm": batch_norm, "conv1d": conv1d, "conv2d": conv2d,
+    "conv3d": conv3d, "gelu": gelu, "group_norm": group_norm, "layer_norm": layer_norm, "leaky_relu": leaky_relu,
+    "linear": linear, "relu": relu, "relu6": relu6, "sigmoid": sigmoid, "silu": silu, "softmax": softmax,
+    "tanh": tanh,
+    "add": simd_add, "sub": simd_sub, "mul": simd_mul, "div": simd_div, "exp": simd_exp, "log": simd_log,
+    "sum": simd_reduce_sum, "mean": simd_reduce_mean, "norm": simd_norm, "square": simd_square,
+    "matmul": matmul, "mm": matmul, "addmm": addmm_mx, "bmm": bmm,
 }
 
 

@@ -255,3 +255,54 @@ def test_ffn_via_inject_pyt_ops_matches_reference_on_cpu(golden_layers2):
     assert torch.nn.Linear is not type(gate) and not issubclass(torch.nn.Linear, mx.Linear)   # restored
     for name, got in (("h", h), ("gate", g_), ("up", u_), ("act", act), ("y", y)):
         assert _same(got, z["ffn_" + name]), name
+
+
+def _layers3():
+    import os
+    import sys
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    if here not in sys.path:
+        sys.path.insert(0, here)
+    import vector_cases as vc
+    return vc, np.load(os.path.join(here, "layers3.npz"))
+
+
+def test_activations_simd_and_norm_layers_match_reference():
+    """Activations (ReLU, ReLU6, LeakyReLU, both GELU forms, sigmoid, tanh, SiLU), the unary and reduction simd
+    operators, LayerNorm, GroupNorm, BatchNorm (training with its running statistics, evaluation) and adaptive
+    average pooling: outputs, every gradient and the updated statistics equal the values recorded from the
+    reference (mx/activations.py, mx/simd_ops.py, mx/norm_utils.py, mx/layernorm.py, mx/groupnorm.py,
+    mx/batchnorm.py, mx/adaptive_avg_pooling.py) under three vector formats, exactly (CPU tensors)."""
+    vc, z = _layers3()
+    n = 0
+    for case in vc.CASES:
+        tensors = {k.split("/", 1)[1]: torch.tensor(z[k]) for k in z.files if k.startswith(case + "/") and k.count("/") == 1}
+        for sname, sdict in vc.SPECS.items():
+            sp = finalize_mx_specs(dict(sdict, custom_cuda=False), early_exit=False)
+            got = vc.run_case(mx, case, tensors, sp)
+            want = {k.rsplit("/", 1)[1]: z[k] for k in z.files if k.startswith("%s/%s/" % (case, sname))}
+            assert set(got) == set(want), (case, sname)
+            for name, g in got.items():
+                assert _same(g, want[name]), (case, sname, name)
+                n += 1
+    assert n > 200
+
+
+def test_full_injection_tables_and_restore():
+    """inject_pyt_ops maps the reference's whole function and module tables (mx/mx_mapping.py:68-122); after
+    restore_pyt_ops the stock callables are back."""
+    import torch.nn.functional as F
+    from microxcaling_b200 import mx_mapping
+    assert len(mx_mapping.FUNCTION_MAPPING) == 30 and len(mx_mapping.MODULE_MAPPING) == 20
+    stock = (torch.sum, torch.exp, F.relu, F.layer_norm, torch.nn.LayerNorm, torch.nn.ReLU)
+    sp = finalize_mx_specs({"bfloat": 16, "custom_cuda": False}, early_exit=False)
+    x = torch.randn(4, 8)
+    with mx_mapping.injected(sp):
+        assert torch.sum is not stock[0] and issubclass(torch.nn.LayerNorm, mx.LayerNorm)
+        y = F.relu(torch.exp(x))
+        s = torch.sum(y, 1)
+        ln = torch.nn.LayerNorm(8)(x)
+    assert (torch.sum, torch.exp, F.relu, F.layer_norm, torch.nn.LayerNorm, torch.nn.ReLU) == stock
+    assert _same(y, mx.relu(mx.simd_exp(x, mx_specs=sp), mx_specs=sp).numpy())
+    assert _same(s, mx.simd_reduce_sum(y, 1, mx_specs=sp).numpy())
+    assert _same(ln, mx.LayerNorm(8, mx_specs=sp)(x).detach().numpy())                 # the MX module's own default eps (1e-12)
