@@ -95,7 +95,7 @@ def run_case(mx, case, t, specs):
     loss = 0
     for k, o in enumerate(outs):
         res["out%d" % k] = o.detach().clone()
-        w = torch.linspace(-1.0, 1.5, o.numel()).reshape(o.shape).to(torch.bfloat16).float() * (k + 1)
+        w = torch.linspace(-1.0, 1.5, o.numel()).reshape(o.shape).to(torch.bfloat16).float().to(o.device) * (k + 1)
         loss = loss + (o * w).sum()
     loss.backward()
     for i, x in enumerate(ins):

@@ -280,3 +280,44 @@ def test_lstm_matches_reference_on_gpu(golden_layers2):
         scale = np.sqrt((b ** 2).mean())
         assert (np.abs(a - b) <= 2.0 ** -5 * (np.abs(b) + scale)).all(), (name, float(np.abs(a - b).max()), scale)
         assert float((a == b).mean()) >= 0.5, (name, float((a == b).mean()))
+
+
+def test_activations_simd_and_norm_layers_on_gpu():
+    """The vector-op layers recorded in layers3.npz (activations, simd operators, LayerNorm, GroupNorm,
+    BatchNorm, adaptive average pooling) on fp32 CUDA tensors with custom_cuda: the same chains with the
+    roundings done by the library's elementwise kernel.  CUDA's exp / tanh / sqrt / division and its reduction
+    order differ from the host's in the last fp32 bit, which moves a value only when it sits on a rounding
+    boundary: at least 97 % of every tensor must be identical and nothing may differ by more than one vector-format
+    step at the scale of the tensor."""
+    import os
+    import sys
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    if here not in sys.path:
+        sys.path.insert(0, here)
+    import vector_cases as vc
+    z = np.load(os.path.join(here, "layers3.npz"))
+
+    class OnGpu:
+        """`mx` with modules moved to the GPU after construction."""
+        def __getattr__(self, name):
+            obj = getattr(mx, name)
+            if isinstance(obj, type) and issubclass(obj, torch.nn.Module):
+                return lambda *a, **k: obj(*a, **k).cuda()
+            return obj
+
+    checked = 0
+    for case in vc.CASES:
+        tensors = {k.split("/", 1)[1]: torch.tensor(z[k]).cuda() for k in z.files
+                   if k.startswith(case + "/") and k.count("/") == 1}
+        for sname in ("bf16", "bf16_even"):
+            sp = finalize_mx_specs(dict(vc.SPECS[sname], custom_cuda=True), early_exit=False)
+            got = vc.run_case(OnGpu(), case, tensors, sp)
+            for name, g in got.items():
+                want = z["%s/%s/%s" % (case, sname, name)].astype(np.float64)
+                a = g.detach().float().cpu().numpy().astype(np.float64)
+                assert a.shape == want.shape, (case, sname, name)
+                step = 2.0 ** -7 * max(np.abs(want).max(), 1e-30)
+                assert np.abs(a - want).max() <= step, (case, sname, name, np.abs(a - want).max(), step)
+                assert (a == want).mean() >= 0.97, (case, sname, name, (a == want).mean())
+                checked += 1
+    assert checked > 120
