@@ -841,19 +841,21 @@ mx_strided_bf16_kernel(const MxArgs a, const int64_t col_tiles, const int64_t nb
             }
         }
         if (CK != CK_NONE && TRANSPOSED && ((bb & 1) || bb + 1 >= kBlocksPerThread || b + 1 >= a.nblk)) {
-            // write out the staged pair of blocks: 4 lanes per output row
-            __syncthreads();
+            // write out the staged pair of blocks: 4 lanes per output row.  A warp stages and writes only its own
+            // 128 columns, so the warps of a CTA never wait for one another and drift out of lock-step.
+            __syncwarp();
             const int nchunk = ((bb & 1) + 1) * 2;
             const int64_t k0 = (bg * kBlocksPerThread + (bb & ~1)) * kMaxRows;
+            const int id0 = (tid & ~31) * 16 + (tid & 31);
 #pragma unroll 4
             for (int it = 0; it < 16; ++it) {
-                const int id = it * kStrBfThreads + tid;
+                const int id = id0 + it * 32;
                 const int c = id >> 2, j = id & 3;
                 if (g0 + c < gcols && j < nchunk)
                     *reinterpret_cast<uint4*>(a.codes + (g0 + c) * padded + k0 + j * 16) =
                         stage[id ^ ((id >> 4) & 7)];
             }
-            __syncthreads();
+            __syncwarp();
         }
     }
     if (CK != CK_NONE && TRANSPOSED && a.sf_gemm && active) {
