@@ -156,30 +156,16 @@ rmsnorm_bf16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__
     // rows of up to kNormKeep * 256 vectors stay in registers between the two passes (one read of x)
     constexpr int kNormKeep = 4;
     const bool keep = vec && hidden / 8 <= (int64_t)kNormKeep * kNormThreads;
-    // `keep` rows are software-pipelined: the next row's loads are issued before the block-wide reduction of
-    // the current one, so they are in flight during the reduction, the normalisation and the stores
-    uint4 kept[kNormKeep], nxt[kNormKeep];
-    if (keep && (int64_t)blockIdx.x < rows) {
-        const uint4* xv = reinterpret_cast<const uint4*>(x + (int64_t)blockIdx.x * hidden);
-#pragma unroll
-        for (int k = 0; k < kNormKeep; ++k) {
-            const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
-            nxt[k] = i < hidden / 8 ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
-        }
-    }
+    uint4 kept[kNormKeep];
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint16_t* xr = x + row * hidden;
         float acc = 0.f;
         if (keep) {
+            const uint4* xv0 = reinterpret_cast<const uint4*>(xr);
 #pragma unroll
-            for (int k = 0; k < kNormKeep; ++k) kept[k] = nxt[k];
-            if (row + gridDim.x < rows) {
-                const uint4* xn = reinterpret_cast<const uint4*>(x + (row + gridDim.x) * hidden);
-#pragma unroll
-                for (int k = 0; k < kNormKeep; ++k) {
-                    const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
-                    nxt[k] = i < hidden / 8 ? __ldg(xn + i) : make_uint4(0, 0, 0, 0);
-                }
+            for (int k = 0; k < kNormKeep; ++k) {
+                const int64_t i = threadIdx.x + (int64_t)k * kNormThreads;
+                kept[k] = i < hidden / 8 ? __ldg(xv0 + i) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int k = 0; k < kNormKeep; ++k) {
@@ -384,7 +370,7 @@ extern "C" int mxq_rmsnorm_bf16(const void* x, const void* weight, const void* b
     if ((hidden & 7) == 0 && (!aligned16(x) || !aligned16(weight) || !aligned16(out) || (bias && !aligned16(bias)) ||
                               (x_norm && !aligned16(x_norm))))
         return MXQ_ERR_BAD_ARG;
-    const unsigned grid = (unsigned)std::min<int64_t>(rows, (int64_t)sm_count() * 8);
+    const unsigned grid = (unsigned)std::min<int64_t>(rows, (int64_t)0x7fffffff);
     rmsnorm_bf16_kernel<<<grid, kNormThreads, 0, (cudaStream_t)stream>>>(
         (const uint16_t*)x, (const uint16_t*)weight, (const uint16_t*)bias, (uint16_t*)out, (uint16_t*)x_norm,
         (uint16_t*)rms_inv, rows, hidden, 1.0f / (float)hidden, eps);
